@@ -18,6 +18,8 @@ What this manager does differently:
   ever read a window therefore never compete for, or waste, each other's pages.
 * A window group gives pages back as soon as every position in them has fallen
   out of the window (`commit`); the block table keeps -1 in their place.
+* A run that reads another run's cache shares that run's pages and block tables; state of
+  fixed size is never shared: every run has the tensors its own layer asked for.
 * Every request also gets a *state slot*: an index into per-run tensors of fixed
   size `[num_slots, ...]` for mixers whose memory does not grow with length.
   The slot's tensors are zeroed when the request registers.
@@ -44,7 +46,8 @@ class PagedView:
 
     group: int                 # index into StepBatch.groups
     keys: torch.Tensor         # [num_pages, kv_heads, page_size, head_dim]
-    values: torch.Tensor       # [num_pages, kv_heads, page_size, value width]
+    values: torch.Tensor | None  # [num_pages, kv_heads, page_size, value width]; None where the
+                               # keys are read as values too (value width 0)
     page_size: int
     window: int | None
     # the group's whole tensor, for tensor maps over keys and values at once; None where keys
@@ -66,7 +69,13 @@ class _Group:
         self.runs = runs
         self.pool = PagePool(num_pages)
         self.page_size = page_size
-        if needs.value_width == needs.head_dim:
+        if needs.value_width == 0:
+            # keys that are read as values too (a cache of latents): one tensor, no values
+            self.storage = None
+            self.keys = torch.zeros((len(runs), num_pages, needs.num_kv_heads, page_size,
+                                     needs.head_dim), dtype=dtype, device=device)
+            self.values = None
+        elif needs.value_width == needs.head_dim:
             self.storage = torch.zeros(
                 (len(runs), 2, num_pages, needs.num_kv_heads, page_size, needs.head_dim),
                 dtype=dtype, device=device)
@@ -125,16 +134,20 @@ class CacheManager:
                 for gi, g in enumerate(self.groups):
                     if run in g.runs:
                         r = g.runs.index(run)
-                        view.paged = PagedView(gi, g.keys[r], g.values[r], page_size,
-                                               g.needs.window, g.storage)
-            if needs.state is not None:
+                        view.paged = PagedView(gi, g.keys[r],
+                                               None if g.values is None else g.values[r],
+                                               page_size, g.needs.window, g.storage)
+            self._views[run] = view
+        for run, (needs, owner) in enumerate(zip(needs_per_run, owner_of_run)):
+            # a run that reads another run's cache shares its pages, not its state
+            if owner is not None:
+                shared = self._views[owner]
+                self._views[run] = CacheView(paged=None if shared is None else shared.paged)
+            view = self._views[run]
+            if view is not None and needs is not None and needs.state is not None:
                 for name, (shape, sdtype) in needs.state.tensors.items():
                     view.state[name] = torch.zeros((max_requests, *shape), dtype=sdtype,
                                                    device=self.device)
-            self._views[run] = view
-        for run, owner in enumerate(owner_of_run):
-            if owner is not None:
-                self._views[run] = self._views[owner]
 
     # ------------------------------------------------------------------ views
     def view(self, run: int) -> CacheView | None:

@@ -1,5 +1,7 @@
 """Configuration: typed architecture configs, the model spec they produce, the registry."""
 
+from .digosun import ARCHITECTURE as DIGOSUN_ARCHITECTURE
+from .digosun import DigosunConfig
 from .qwen2 import ARCHITECTURE as QWEN2_ARCHITECTURE
 from .qwen2 import ConfigError, Qwen2Config
 from .registry import (config_class_for, load_config, register_architecture,
@@ -7,7 +9,9 @@ from .registry import (config_class_for, load_config, register_architecture,
 from .spec import LayerSpec, ModelSpec, PartSpec, RunSpec
 
 register_architecture(QWEN2_ARCHITECTURE, Qwen2Config)
+register_architecture(DIGOSUN_ARCHITECTURE, DigosunConfig)
 
-__all__ = ["ConfigError", "Qwen2Config", "QWEN2_ARCHITECTURE", "LayerSpec", "ModelSpec",
+__all__ = ["ConfigError", "Qwen2Config", "QWEN2_ARCHITECTURE", "DigosunConfig",
+           "DIGOSUN_ARCHITECTURE", "LayerSpec", "ModelSpec",
            "PartSpec", "RunSpec", "config_class_for", "load_config",
            "register_architecture", "supported_architectures", "unregister_architecture"]

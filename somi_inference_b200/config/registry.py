@@ -57,7 +57,16 @@ def load_config(model_dir: str):
         raise FileNotFoundError(f"{model_dir!r} holds no config.json")
     with open(path, "r", encoding="utf-8") as f:
         raw = json.load(f)
+    return config_class_for(architecture_name(raw, path)).from_dict(raw)
+
+
+def architecture_name(raw: dict[str, Any], where: str = "config.json") -> str:
+    """The name a config.json gives its architecture: the first entry of an `architectures`
+    list, or the string under `architecture`."""
     archs = raw.get("architectures")
-    if not archs or not isinstance(archs, list):
-        raise ValueError(f"{path}: no 'architectures' list; supported: {supported_architectures()}")
-    return config_class_for(archs[0]).from_dict(raw)
+    if isinstance(archs, list) and archs:
+        return archs[0]
+    if isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
+    raise ValueError(f"{where}: neither an 'architectures' list nor an 'architecture' name; "
+                     f"supported: {supported_architectures()}")

@@ -36,6 +36,11 @@ class LayerSpec:
     pre-norm arrangement wants "mixer" and "feed_forward"; an arrangement that also normalises
     what its parts return can name four.  The arrangement's constructor is called with
     `(mixer, feed_forward, norms)`, `norms` being a dict from those names to built norms.
+
+    `extras` are further parts of the layer that are neither of these (a gate on a residual
+    branch, a short convolution in front of the mixer, ...), each under the name by which the
+    arrangement asks for it and looked up in the registry of layer extras; an arrangement of a
+    layer that has some is built with `(mixer, feed_forward, norms, extras)`.
     """
 
     prefix: str  # e.g. "model.layers.3"
@@ -43,6 +48,7 @@ class LayerSpec:
     feed_forward: PartSpec | None
     norms: Mapping[str, PartSpec] = field(default_factory=dict)
     arrangement: str = "pre_norm"
+    extras: Mapping[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -25,13 +25,19 @@ constexpr int kSgThreads = 256;
 template <int BM>
 __global__ void __launch_bounds__(kSgThreads)
 sgemm_nt_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                const float* __restrict__ bias, float* __restrict__ y, int M, int N, int K) {
+                const float* __restrict__ bias, float* __restrict__ y, int M, int N, int K,
+                long long ldx, long long ldy, long long bsx, long long bsw, long long bsy, int vec4) {
     constexpr int TM = BM / 16;          // rows per thread
     constexpr int TN = kSgBN / 16;       // columns per thread (8)
     __shared__ __align__(16) float xs[kSgBK][BM];
     __shared__ __align__(16) float ws[kSgBK][kSgBN];
     pdl_launch_dependents();
     pdl_wait();
+    // blockIdx.z is the product's index in a batch: operands of product b start b * bs{x,w,y}
+    // elements further on; rows of x and y lie ldx and ldy elements apart (w's rows K)
+    x += blockIdx.z * bsx;
+    w += blockIdx.z * bsw;
+    y += blockIdx.z * bsy;
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * kSgBN;
     const int tr = tid / 16, tc = tid % 16;       // this thread's rows tr*TM.., columns tc*TN..
@@ -40,7 +46,7 @@ sgemm_nt_kernel(const float* __restrict__ x, const float* __restrict__ w,
     for (int i = 0; i < TM; ++i)
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
-    const bool vec = (K & 3) == 0;
+    const bool vec = vec4 != 0;
     // loading: a slice is BM (or 128) rows of 8 floats = two float4 per row
     for (int k0 = 0; k0 < K; k0 += kSgBK) {
         for (int idx = tid; idx < BM * 2; idx += kSgThreads) {
@@ -48,7 +54,7 @@ sgemm_nt_kernel(const float* __restrict__ x, const float* __restrict__ w,
             const int gm = m0 + r, gk = k0 + h;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (gm < M) {
-                const float* p = x + static_cast<size_t>(gm) * K + gk;
+                const float* p = x + static_cast<size_t>(gm) * ldx + gk;
                 if (vec && gk + 3 < K) v = *reinterpret_cast<const float4*>(p);
                 else {
                     if (gk < K) v.x = p[0];
@@ -100,7 +106,7 @@ sgemm_nt_kernel(const float* __restrict__ x, const float* __restrict__ w,
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const int gn = n0 + tc * TN + j;
-            if (gn < N) y[static_cast<size_t>(gm) * N + gn] = acc[i][j] + (bias ? bias[gn] : 0.f);
+            if (gn < N) y[static_cast<size_t>(gm) * ldy + gn] = acc[i][j] + (bias ? bias[gn] : 0.f);
         }
     }
 }
@@ -109,20 +115,31 @@ sgemm_nt_kernel(const float* __restrict__ x, const float* __restrict__ w,
 
 using namespace somi;
 
-// y[M, N] = x[M, K] w[N, K]^T (+ bias), all float32, row-major.
-SOMI_API int somi_gemm_f32(const float* x, const float* w, const float* bias, float* y, int M, int N,
-                           int K, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
-    if (K <= 0) return SOMI_ERR_UNSUPPORTED;
+// y_b[M, N] = x_b[M, K] w_b[N, K]^T (+ bias) for b in [0, batch), all float32.  Rows of x_b and y_b lie
+// ldx and ldy elements apart, rows of w_b K; product b's operands start b * bs{x,w,y} elements
+// after product 0's (so the heads of a [tokens, heads, width] tensor are a batch without a copy).
+SOMI_API int somi_gemm_f32_batched(const float* x, const float* w, const float* bias, float* y, int M,
+                                   int N, int K, int batch, long long ldx, long long ldy,
+                                   long long bsx, long long bsw, long long bsy, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || batch > 65535 || ldx < K || ldy < N) return SOMI_ERR_UNSUPPORTED;
+    const int vec4 = ((K | ldx | bsx | bsw) & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
     const unsigned tiles_n = static_cast<unsigned>((N + kSgBN - 1) / kSgBN);
     if (M <= 32) {
-        launch_pdl(sgemm_nt_kernel<32>, dim3(tiles_n, (M + 31) / 32), dim3(kSgThreads), 0, stream, x, w,
-                   bias, y, M, N, K);
+        launch_pdl(sgemm_nt_kernel<32>, dim3(tiles_n, (M + 31) / 32, batch), dim3(kSgThreads), 0, stream,
+                   x, w, bias, y, M, N, K, ldx, ldy, bsx, bsw, bsy, vec4);
     } else {
         const unsigned tiles_m = static_cast<unsigned>((M + 127) / 128);
         if (tiles_m > 65535u) return SOMI_ERR_UNSUPPORTED;
-        launch_pdl(sgemm_nt_kernel<128>, dim3(tiles_n, tiles_m), dim3(kSgThreads), 0, stream, x, w,
-                   bias, y, M, N, K);
+        launch_pdl(sgemm_nt_kernel<128>, dim3(tiles_n, tiles_m, batch), dim3(kSgThreads), 0, stream,
+                   x, w, bias, y, M, N, K, ldx, ldy, bsx, bsw, bsy, vec4);
     }
     return launch_status();
+}
+
+// y[M, N] = x[M, K] w[N, K]^T (+ bias), all float32, row-major.
+SOMI_API int somi_gemm_f32(const float* x, const float* w, const float* bias, float* y, int M, int N,
+                           int K, cudaStream_t stream) {
+    return somi_gemm_f32_batched(x, w, bias, y, M, N, K, 1, K, N, 0, 0, 0, stream);
 }

@@ -1,0 +1,326 @@
+// Kernels of layer parts that are not attention and not a matrix product:
+//   * token embedding + sinusoidal position vector + layer norm -> float32 residual stream
+//   * gated residual sum + layer norm (weight, no bias)
+//   * short causal convolution over time with a per-request state of the last inputs
+//   * RMS norm of the two latents of a latent-attention mixer, the key/value latent written to
+//     its cache slot
+//   * the xIELU activation
+// Everything a norm, a gate or a position computes is float32; inputs and outputs are float32 or
+// bfloat16.  One CTA per token (row) unless stated otherwise.
+#include "common.cuh"
+
+namespace somi {
+
+template <typename T> __device__ __forceinline__ float ld_f(const T* p, size_t i) { return to_float(p[i]); }
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// Mean and inverse standard deviation of the H floats in `buf` (shared memory), two passes:
+// the variance is the mean of the squared deviations from the mean.
+__device__ __forceinline__ void mean_rstd(const float* buf, int H, float eps, float* scratch,
+                                          float& mean, float& rstd) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) s += buf[i];
+    mean = block_sum(s, scratch) / static_cast<float>(H);
+    float v = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float d = buf[i] - mean;
+        v = fmaf(d, d, v);
+    }
+    rstd = 1.0f / sqrtf(block_sum(v, scratch) / static_cast<float>(H) + eps);
+}
+
+// ------------------------------------------- embedding + sinusoid + layer norm
+// x = table[ids[t]] + s(positions[t]);  s[2i] = sin(p * inv_freq[i]), s[2i+1] = cos(same angle)
+// (inv_freq[i] = base^(-2i/H), made on the host);
+// residual[t] = (x - mean) * rstd * weight.
+template <typename T>
+__global__ void embed_sinusoid_layernorm_kernel(const int* __restrict__ ids,
+                                                const int* __restrict__ positions,
+                                                const T* __restrict__ table,
+                                                const float* __restrict__ inv_freq,
+                                                const void* __restrict__ weight, int weight_dtype,
+                                                float eps, float* __restrict__ out, int H) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const T* row = table + static_cast<size_t>(ids[t]) * H;
+    const float p = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float angle = p * inv_freq[i >> 1];      // float32, rounded once
+        row_buf[i] = to_float(row[i]) + ((i & 1) ? cosf(angle) : sinf(angle));
+    }
+    __syncthreads();
+    float mean, rstd;
+    mean_rstd(row_buf, H, eps, scratch, mean, rstd);
+    float* o = out + static_cast<size_t>(t) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = (row_buf[i] - mean) * rstd * load_as_float(weight, weight_dtype, i);
+}
+
+// ------------------------------------------------ gated residual + layer norm
+// r = residual[row] + g * sum_s delta[s][row], g = sigmoid(gate[row]) (1 without a gate);
+// if write_back: residual[row] = r;  out[b] = (r - mean) * rstd * weight  (rms = 1: r * rrms * weight),
+// row = rows ? rows[b] : b.  delta: [splits] partial sums `split_stride` elements apart, added in order.
+template <typename TD, typename TG, typename TO>
+__global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                     int splits, long long split_stride,
+                                     const TG* __restrict__ gate, long long gate_stride,
+                                     const void* __restrict__ weight, int weight_dtype, float eps,
+                                     TO* __restrict__ out, const int* __restrict__ rows, int H,
+                                     int write_back, int rms) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
+    float* r = residual + row * H;
+    const TD* d = delta ? delta + row * H : nullptr;
+    const TG* g = gate ? gate + row * gate_stride : nullptr;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (d) {
+            float sum = to_float(d[i]);
+            for (int sp = 1; sp < splits; ++sp) sum += to_float(d[sp * split_stride + i]);
+            if (g) sum *= sigmoid_f(to_float(g[i]));
+            v += sum;
+            if (write_back) r[i] = v;
+        }
+        row_buf[i] = v;
+    }
+    __syncthreads();
+    float mean = 0.f, rstd;
+    if (rms) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) ss = fmaf(row_buf[i], row_buf[i], ss);
+        rstd = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(H) + eps);
+    } else {
+        mean_rstd(row_buf, H, eps, scratch, mean, rstd);
+    }
+    TO* o = out + static_cast<size_t>(b) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_float<TO>((row_buf[i] - mean) * rstd * load_as_float(weight, weight_dtype, i));
+}
+
+// ------------------------------------------------- short causal convolution
+// out[t] = h[t] + sum_{d=0}^{taps-1} w[:, taps-1-d] * h_(t-d), where h_(t-d) is the row d places
+// back in the same request: a row of this step, or (before the step's first row) the request's
+// state, which holds its last taps-1 inputs, oldest first, zero before the sequence's start.
+// The state is only read here; `causal_taps_state_kernel` moves it on afterwards.
+template <typename T>
+__global__ void causal_taps_kernel(const T* __restrict__ h, const float* __restrict__ w,
+                                   const T* __restrict__ state, const int* __restrict__ cu_q,
+                                   const int* __restrict__ token_request,
+                                   const int* __restrict__ state_slot, T* __restrict__ out, int H,
+                                   int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int req = token_request[t];
+    const int local = t - cu_q[req];
+    const T* st = state + static_cast<size_t>(state_slot[req]) * (taps - 1) * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float own = to_float(h[static_cast<size_t>(t) * H + c]);
+        float acc = 0.f;
+        for (int d = taps - 1; d >= 0; --d) {          // oldest input first
+            float v;
+            if (d == 0) v = own;
+            else if (local - d >= 0) v = to_float(h[static_cast<size_t>(t - d) * H + c]);
+            else v = to_float(st[static_cast<size_t>(taps - 1 + local - d) * H + c]);
+            acc = fmaf(w[static_cast<size_t>(c) * taps + (taps - 1 - d)], v, acc);
+        }
+        out[static_cast<size_t>(t) * H + c] = from_float<T>(own + acc);
+    }
+}
+
+// New state of request r: its last taps-1 inputs after this step's rows, oldest first.  A thread
+// owns one channel of one request and reads what it needs of the old state before it writes.
+constexpr int kMaxTaps = 32;
+template <typename T>
+__global__ void causal_taps_state_kernel(const T* __restrict__ h, T* __restrict__ state,
+                                         const int* __restrict__ cu_q,
+                                         const int* __restrict__ state_slot, int H, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int req = blockIdx.x;
+    const int first = cu_q[req], q = cu_q[req + 1] - first;
+    const int keep = taps - 1;
+    T* st = state + static_cast<size_t>(state_slot[req]) * keep * H;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H; c += gridDim.y * blockDim.x) {
+        T v[kMaxTaps];
+        for (int s = 0; s < keep; ++s) {
+            const int local = q - keep + s;        // row of this step, or (negative) of the old state
+            v[s] = local >= 0 ? h[static_cast<size_t>(first + local) * H + c]
+                              : st[static_cast<size_t>(keep + local) * H + c];
+        }
+        for (int s = 0; s < keep; ++s) st[static_cast<size_t>(s) * H + c] = v[s];
+    }
+}
+
+// ------------------------------------------ RMS norm of latents + cache write
+// x[t] = [a (na columns) | b (nb columns)], rows `stride` elements apart.  a_out[t] = rmsnorm(a) * wa;
+// rmsnorm(b) * wb goes to cache + slot_map[t] * nb (and nowhere when nb == 0).  One warp per part.
+template <typename T>
+__global__ void latent_norm_store_kernel(const T* __restrict__ x, long long stride, int na, int nb,
+                                         const void* __restrict__ wa, const void* __restrict__ wb,
+                                         int weight_dtype, float eps, T* __restrict__ a_out,
+                                         const int* __restrict__ slot_map, T* __restrict__ cache) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 1 && nb == 0) return;
+    const T* src = x + static_cast<size_t>(t) * stride + (warp == 0 ? 0 : na);
+    const int n = warp == 0 ? na : nb;
+    const void* w = warp == 0 ? wa : wb;
+    T* dst = warp == 0 ? a_out + static_cast<size_t>(t) * na
+                       : cache + static_cast<size_t>(slot_map[t]) * nb;
+    float ss = 0.f;
+    for (int i = lane; i < n; i += 32) {
+        const float v = to_float(src[i]);
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(n) + eps);
+    for (int i = lane; i < n; i += 32)
+        dst[i] = from_float<T>(to_float(src[i]) * inv * load_as_float(w, weight_dtype, i));
+}
+
+// ---------------------------------------------------------------- xIELU
+// z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2; (p, q) = act[0..1].
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ x, long long stride, const void* __restrict__ act,
+                             int act_dtype, T* __restrict__ out, int n) {
+    pdl_launch_dependents();
+    const float ap = softplus_f(load_as_float(act, act_dtype, 0));        // [constant]
+    const float aq = 0.5f + softplus_f(load_as_float(act, act_dtype, 1));  // [constant]
+    pdl_wait();
+    const T* src = x + static_cast<size_t>(blockIdx.x) * stride;
+    T* dst = out + static_cast<size_t>(blockIdx.x) * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float z = to_float(src[i]);
+        const float y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
+        dst[i] = from_float<T>(y);
+    }
+}
+
+inline int row_threads(int H) { return H >= 4096 ? 512 : (H >= 1024 ? 256 : 128); }
+
+}  // namespace somi
+
+using namespace somi;
+
+SOMI_API int somi_embed_sinusoid_layernorm(const int* ids, const int* positions, const void* table,
+                                           int dtype, const float* inv_freq, const void* weight, int weight_dtype,
+                                           float eps, float* out, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t smem = static_cast<size_t>(H) * sizeof(float);
+    if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
+#define SOMI_LAUNCH_EMB(TT)                                                                      \
+    do {                                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            cudaFuncSetAttribute(embed_sinusoid_layernorm_kernel<TT>,                            \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        launch_pdl(embed_sinusoid_layernorm_kernel<TT>, dim3(T), dim3(row_threads(H)), smem,     \
+                   stream, ids, positions, static_cast<const TT*>(table), inv_freq, weight,      \
+                   weight_dtype, eps, out, H);                                                   \
+    } while (0)
+    if (dtype == SOMI_F32) SOMI_LAUNCH_EMB(float);
+    else SOMI_LAUNCH_EMB(__nv_bfloat16);
+#undef SOMI_LAUNCH_EMB
+    return launch_status();
+}
+
+SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dtype, int delta_splits,
+                                long long delta_split_stride, const void* gate, int gate_dtype,
+                                long long gate_stride, const void* weight, int weight_dtype, float eps,
+                                void* out, int out_dtype, const int* rows, int n_out, int H,
+                                int write_back, int rms, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if (delta_splits < 1 || (delta_splits > 1 && delta_dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
+    if (gate && !delta) return SOMI_ERR_UNSUPPORTED;
+    const size_t smem = static_cast<size_t>(H) * sizeof(float);
+    if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
+    if (!gate) gate_dtype = out_dtype;
+#define SOMI_LAUNCH_LN(TD, TG, TO)                                                               \
+    do {                                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            cudaFuncSetAttribute(add_layernorm_kernel<TD, TG, TO>,                               \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        launch_pdl(add_layernorm_kernel<TD, TG, TO>, dim3(n_out), dim3(row_threads(H)), smem,    \
+                   stream, residual, static_cast<const TD*>(delta), delta_splits,                \
+                   delta_split_stride, static_cast<const TG*>(gate), gate_stride, weight,        \
+                   weight_dtype, eps, static_cast<TO*>(out), rows, H, write_back, rms);          \
+    } while (0)
+    // the gate and the output are of the compute dtype; the delta is that or float32 partial sums
+    if (out_dtype == SOMI_F32) {
+        if (delta_dtype != SOMI_F32 || gate_dtype != SOMI_F32) return SOMI_ERR_UNSUPPORTED;
+        SOMI_LAUNCH_LN(float, float, float);
+    } else {
+        if (gate_dtype != SOMI_BF16) return SOMI_ERR_UNSUPPORTED;
+        if (delta_dtype == SOMI_F32) SOMI_LAUNCH_LN(float, __nv_bfloat16, __nv_bfloat16);
+        else SOMI_LAUNCH_LN(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    }
+#undef SOMI_LAUNCH_LN
+    return launch_status();
+}
+
+SOMI_API int somi_causal_taps_max() { return kMaxTaps; }
+
+// h, out: [T, H]; w: float32 [H, taps]; state: [slots, taps - 1, H] of h's dtype.
+SOMI_API int somi_causal_taps(const void* h, int dtype, const float* w, void* state, const int* cu_q,
+                              const int* token_request, const int* state_slot, void* out, int T,
+                              int R, int H, int taps, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (taps < 1 || taps > kMaxTaps || R <= 0) return SOMI_ERR_UNSUPPORTED;
+    const int threads = min(1024, ((H + 31) / 32) * 32);
+    const int tb = min(256, threads);
+    const int chunks = max(1, min(64, (H + tb - 1) / tb));
+#define SOMI_LAUNCH_TAPS(TT)                                                                     \
+    do {                                                                                         \
+        launch_pdl(causal_taps_kernel<TT>, dim3(T), dim3(min(threads, 256)), 0, stream,          \
+                   static_cast<const TT*>(h), w, static_cast<const TT*>(state), cu_q,            \
+                   token_request, state_slot, static_cast<TT*>(out), H, taps);                   \
+        if (taps > 1)                                                                            \
+            launch_pdl(causal_taps_state_kernel<TT>, dim3(R, chunks), dim3(tb), 0, stream,       \
+                       static_cast<const TT*>(h), static_cast<TT*>(state), cu_q, state_slot, H,  \
+                       taps);                                                                    \
+    } while (0)
+    if (dtype == SOMI_F32) SOMI_LAUNCH_TAPS(float);
+    else SOMI_LAUNCH_TAPS(__nv_bfloat16);
+#undef SOMI_LAUNCH_TAPS
+    return launch_status();
+}
+
+SOMI_API int somi_latent_norm_store(const void* x, int dtype, long long stride, int na, int nb,
+                                    const void* wa, const void* wb, int weight_dtype, float eps,
+                                    void* a_out, const int* slot_map, void* cache, int T,
+                                    cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (na <= 0 || nb < 0 || (nb > 0 && (!slot_map || !cache))) return SOMI_ERR_UNSUPPORTED;
+#define SOMI_LAUNCH_LAT(TT)                                                                      \
+    launch_pdl(latent_norm_store_kernel<TT>, dim3(T), dim3(64), 0, stream,                       \
+               static_cast<const TT*>(x), stride, na, nb, wa, wb, weight_dtype, eps,             \
+               static_cast<TT*>(a_out), slot_map, static_cast<TT*>(cache))
+    if (dtype == SOMI_F32) SOMI_LAUNCH_LAT(float);
+    else SOMI_LAUNCH_LAT(__nv_bfloat16);
+#undef SOMI_LAUNCH_LAT
+    return launch_status();
+}
+
+SOMI_API int somi_xielu(const void* x, int dtype, long long stride, const void* act, int act_dtype,
+                        void* out, int T, int n, cudaStream_t stream) {
+    if (T <= 0 || n <= 0) return 0;
+    const int threads = min(1024, max(128, ((n / 8 + 31) / 32) * 32));
+    if (dtype == SOMI_F32)
+        launch_pdl(xielu_kernel<float>, dim3(T), dim3(threads), 0, stream,
+                   static_cast<const float*>(x), stride, act, act_dtype, static_cast<float*>(out), n);
+    else
+        launch_pdl(xielu_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+                   static_cast<const __nv_bfloat16*>(x), stride, act, act_dtype,
+                   static_cast<__nv_bfloat16*>(out), n);
+    return launch_status();
+}

@@ -69,13 +69,10 @@ def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
 
 
 def _typed_config(path: str):
-    from ..config.registry import config_class_for
+    from ..config.registry import architecture_name, config_class_for
     with open(path) as f:
         raw = json.load(f)
-    archs = raw.get("architectures")
-    if not archs:
-        raise ValueError(f"{path}: no 'architectures' list")
-    return config_class_for(archs[0]).from_dict(raw)
+    return config_class_for(architecture_name(raw, path)).from_dict(raw)
 
 
 def main(argv: list[str] | None = None, *, ops=None, device=None) -> int:

@@ -21,7 +21,7 @@ import os
 import sys
 
 TRACE_PAGE_SIZE = 16       # divides 64, so a request's pages never exceed its count rounded up to 64
-MAX_LIVE_REQUESTS = 16
+MAX_LIVE_REQUESTS = 4        # state slots: no more requests are live at any time
 
 
 def main(argv: list[str] | None = None) -> int:
@@ -32,6 +32,8 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=TRACE_PAGE_SIZE)
+    ap.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS,
+                    help="state slots: the most requests that are live at any time")
     args = ap.parse_args(argv)
 
     os.makedirs(args.out, exist_ok=True)
@@ -42,7 +44,7 @@ def main(argv: list[str] | None = None) -> int:
     unit = -(-unit // page) * page
     pool_tokens = -(-args.max_tokens // unit) * unit
     engine = Engine(args.model, dtype=args.dtype, page_size=page, max_tokens=pool_tokens,
-                    max_requests=MAX_LIVE_REQUESTS)
+                    max_requests=args.max_requests)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -65,8 +65,12 @@ class CudaOps:
         self.prefill_tc_q_tile = int(self.lib.somi_prefill_tc_q_tile())
         self.lib.somi_prefill_pp_q_tile.restype = ctypes.c_int
         self.prefill_pp_q_tile = int(self.lib.somi_prefill_pp_q_tile())
-        self.q_tile_sizes = (self.generic_q_tile, self.prefill_q_tile, self.prefill_tc_q_tile,
-                             self.prefill_pp_q_tile)
+        self.lib.somi_latent_attention_generic_q_tile.restype = ctypes.c_int
+        self.latent_q_tile = int(self.lib.somi_latent_attention_generic_q_tile())
+        self.q_tile_sizes = tuple(dict.fromkeys((
+            self.generic_q_tile, self.prefill_q_tile, self.prefill_tc_q_tile,
+            self.prefill_pp_q_tile, self.latent_q_tile)))
+        self.max_taps = int(self.lib.somi_causal_taps_max())
         self.use_pp_prefill = True
         self.pp_prefill_min_ctas = torch.cuda.get_device_properties(0).multi_processor_count
         self.use_tc_prefill = True
@@ -416,6 +420,180 @@ class CudaOps:
                                                  batch.num_requests, nq, nkv, hd,
                                                  qkv.element_size(), win),
                            detail="with merge" if max_splits > 1 else "")
+
+    # ------------------------------------------------ gated layers, latent attention
+    def embed_sinusoid_layernorm(self, ids, positions, table, inv_freq, weight, eps, out) -> None:
+        """out = layernorm(table[ids] + sinusoid(positions)) * weight, float32 [T, H]."""
+        _check(ids, positions, table, inv_freq, weight, out)
+        assert ids.dtype == torch.int32 and positions.dtype == torch.int32
+        assert out.dtype == torch.float32 and inv_freq.dtype == torch.float32
+        assert inv_freq.numel() * 2 == table.shape[1]
+        rc = self.lib.somi_embed_sinusoid_layernorm(
+            _ptr(ids), _ptr(positions), _ptr(table), _code(table), _ptr(inv_freq), _ptr(weight),
+            _code(weight), ctypes.c_float(eps), _ptr(out), ctypes.c_int(ids.shape[0]),
+            ctypes.c_int(table.shape[1]), self._stream())
+        self._done(rc, "embed_sinusoid_layernorm")
+        if trace.active():
+            trace.note("embed_sinusoid_layernorm", ids.shape[0] * table.shape[1] * (table.element_size() + 4))
+
+    def add_layernorm(self, residual, delta, gate, weight, eps, out, rows=None, rms=False) -> None:
+        """residual += sigmoid(gate) * delta (float32, in place; no gate: plain sum);
+        out = layernorm(residual) * weight (mean taken off; with `rms`, an RMS norm instead).
+
+        `delta`: [N, H] in the compute dtype, or float32 [splits, N, H] partial sums added in
+        order.  `gate`: logits [N, H] whose rows may lie further apart (a view of a wider
+        product).  With `rows`, only those rows are produced and residual is not written."""
+        _check(residual, delta, weight, out, rows)
+        assert residual.dtype == torch.float32
+        H = residual.shape[1]
+        n_out = out.shape[0]
+        splits, stride = 1, 0
+        if delta is not None and delta.dim() == 3:
+            assert delta.dtype == torch.float32
+            splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+        gate_stride = 0
+        if gate is not None:
+            if not gate.is_cuda or gate.stride(1) != 1 or gate.shape != (residual.shape[0], H):
+                raise KernelError("a gate is [rows, H] with contiguous rows")
+            gate_stride = gate.stride(0)
+        rc = self.lib.somi_add_layernorm(
+            _ptr(residual), _ptr(delta), _code(delta) if delta is not None else _code(out),
+            ctypes.c_int(splits), ctypes.c_longlong(stride), _ptr(gate),
+            _code(gate) if gate is not None else _code(out), ctypes.c_longlong(gate_stride),
+            _ptr(weight), _code(weight), ctypes.c_float(eps), _ptr(out), _code(out), _ptr(rows),
+            ctypes.c_int(n_out), ctypes.c_int(H), ctypes.c_int(0 if rows is not None else 1),
+            ctypes.c_int(1 if rms else 0), self._stream())
+        self._done(rc, "add_layernorm")
+        if trace.active():
+            n = n_out * H
+            moved = n * (4 + out.element_size()) + H * weight.element_size()
+            if delta is not None:
+                moved += splits * n * delta.element_size()
+            if gate is not None:
+                moved += n * gate.element_size()
+            if rows is None:
+                moved += n * 4
+            trace.note("add_layernorm", moved, detail=f"splits={splits}" if splits > 1 else "")
+
+    def check_taps(self, taps: int) -> None:
+        if not 1 <= taps <= self.max_taps:
+            raise KernelError(f"a causal convolution of {taps} taps is not supported (1 to "
+                              f"{self.max_taps})")
+
+    def causal_taps(self, h, weight, state, batch, out) -> None:
+        """out = h + conv(h) over each request's rows, continued from `state` [slots, taps-1, H]
+        (the request's last inputs), which is moved on by this step's rows."""
+        _check(h, weight, state, out)
+        taps = weight.shape[1]
+        assert weight.dtype == torch.float32 and weight.shape[0] == h.shape[1]
+        if taps > 1:
+            assert state is not None and state.dtype == h.dtype
+            assert tuple(state.shape[1:]) == (taps - 1, h.shape[1])
+        rc = self.lib.somi_causal_taps(
+            _ptr(h), _code(h), _ptr(weight), _ptr(state), _ptr(batch.cu_q),
+            _ptr(batch.token_request), _ptr(batch.state_slot), _ptr(out), ctypes.c_int(h.shape[0]),
+            ctypes.c_int(batch.num_requests), ctypes.c_int(h.shape[1]), ctypes.c_int(taps),
+            self._stream())
+        self._done(rc, "causal_taps")
+        if taps > 1:
+            self.launches += 1
+        if trace.active():
+            trace.note("causal_taps", 2 * h.numel() * h.element_size()
+                       + 2 * batch.num_requests * (taps - 1) * h.shape[1] * h.element_size())
+
+    def latent_norm_store(self, x, na, nb, wa, wb, eps, a_out, slot_map, cache) -> None:
+        """x = [a | b] per row: a_out = rmsnorm(a) * wa; rmsnorm(b) * wb goes to the cache slot of
+        the row's token (`nb` = 0: there is no b)."""
+        _check(x, wa, wb, a_out, slot_map, cache)
+        assert x.shape[1] == na + nb and a_out.dtype == x.dtype
+        if nb:
+            assert cache.dtype == x.dtype and cache.shape[-1] == nb and cache.shape[1] == 1
+            assert wb.dtype == wa.dtype
+        rc = self.lib.somi_latent_norm_store(
+            _ptr(x), _code(x), ctypes.c_longlong(x.shape[1]), ctypes.c_int(na), ctypes.c_int(nb),
+            _ptr(wa), _ptr(wb), _code(wa), ctypes.c_float(eps), _ptr(a_out), _ptr(slot_map),
+            _ptr(cache), ctypes.c_int(x.shape[0]), self._stream())
+        self._done(rc, "latent_norm_store")
+        if trace.active():
+            trace.note("latent_norm_store", 2 * x.numel() * x.element_size())
+
+    def xielu(self, x, n, act, out) -> None:
+        """out[:, :n] = xielu(x[:, :n]) with (p, q) = act; x's rows may be wider than n."""
+        _check(x, act, out)
+        assert out.shape == (x.shape[0], n) and out.dtype == x.dtype and x.shape[1] >= n
+        rc = self.lib.somi_xielu(_ptr(x), _code(x), ctypes.c_longlong(x.shape[1]), _ptr(act),
+                                 _code(act), _ptr(out), ctypes.c_int(x.shape[0]), ctypes.c_int(n),
+                                 self._stream())
+        self._done(rc, "xielu")
+        if trace.active():
+            trace.note("xielu", 2 * out.numel() * out.element_size())
+
+    def head_product(self, x: torch.Tensor, w: torch.Tensor, heads_first: bool) -> torch.Tensor:
+        """A product per head: y_h = x_h @ w_h^T with w [heads, N, K].
+
+        `heads_first`: x is [T, heads, K] (a view of a [T, heads * K] projection) and y comes
+        back as [heads, T, N]; otherwise x is [heads, T, K] and y is [T, heads, N], so that the
+        next projection reads [T, heads * N] without a copy.  float32: the engine's own product,
+        batched over heads; bfloat16: the library's batched product."""
+        H, N, K = w.shape
+        if heads_first:
+            T = x.shape[0]
+            xs = x.transpose(0, 1)                               # [H, T, K] view
+            y = torch.empty((H, T, N), dtype=x.dtype, device=x.device)
+            ys = y
+        else:
+            T = x.shape[1]
+            xs = x
+            y = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
+            ys = y.transpose(0, 1)                               # [H, T, N] view
+        assert xs.shape == (H, T, K) and xs.stride(2) == 1 and w.is_contiguous()
+        if x.dtype == torch.float32:
+            rc = self.lib.somi_gemm_f32_batched(
+                _ptr(xs), _ptr(w), None, _ptr(ys), ctypes.c_int(T), ctypes.c_int(N),
+                ctypes.c_int(K), ctypes.c_int(H), ctypes.c_longlong(xs.stride(1)),
+                ctypes.c_longlong(ys.stride(1)), ctypes.c_longlong(xs.stride(0)),
+                ctypes.c_longlong(N * K), ctypes.c_longlong(ys.stride(0)), self._stream())
+            self._done(rc, "gemm_f32_batched")
+            name = "gemm_f32_batched"
+        else:
+            torch.bmm(xs, w.transpose(1, 2), out=ys)
+            name = "library_gemm_batched"
+        if trace.active():
+            trace.note(name, (H * N * K + 2 * T * H * K) * x.element_size(), 2.0 * T * H * N * K,
+                       detail=f"heads={H} M={T} N={N} K={K}")
+        return y
+
+    def check_latent_geometry(self, heads: int, rank: int) -> None:
+        if not (1 <= rank <= 512 and 1 <= heads <= 65535):
+            raise KernelError(f"latent attention over a latent of {rank} elements with {heads} "
+                              "heads is not supported (latent up to 512)")
+
+    def latent_attention(self, q, cache, batch, group, heads, rank, scale, window, sinks, out) -> None:
+        """Attention of every token of the step over a cache of latents that serve as keys and
+        as values for every head (`q`, `out`: [heads, T, rank]; cache [pages, 1, page, rank]);
+        `sinks`: float32 [heads] scores that join every softmax's denominator, or None."""
+        _check(q, cache, out, group.block_table, sinks)
+        assert q.dtype == cache.dtype == out.dtype and q.shape == out.shape == (heads, q.shape[1], rank)
+        assert cache.shape[1] == 1 and cache.shape[3] == rank
+        assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads)
+        page_size = cache.shape[2]
+        T = q.shape[1]
+        tiles = batch.tiles[self.latent_q_tile]
+        n_decode = batch.num_requests - batch.num_prefill_requests
+        rc = self.lib.somi_latent_attention_generic(
+            _ptr(q), _code(q), ctypes.c_longlong(rank), ctypes.c_longlong(T * rank), _ptr(cache),
+            _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+            _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+            ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
+            ctypes.c_int(n_decode), ctypes.c_int(heads), ctypes.c_int(rank),
+            ctypes.c_int(page_size), ctypes.c_float(scale), ctypes.c_int(int(window) if window else 0),
+            _ptr(sinks), _ptr(out), ctypes.c_longlong(rank), ctypes.c_longlong(T * rank),
+            self._stream())
+        self._done(rc, "latent_attention")
+        if trace.active():
+            moved, flops = self._attention_work(batch, 0, batch.num_requests, heads, 1, rank,
+                                                q.element_size(), int(window) if window else 0)
+            trace.note("latent_attention_generic", moved / 2 + heads * T * rank * q.element_size(), flops)
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
         """out = silu(gate) * up; gate/up are the two halves of `gu`'s rows, or alternate."""

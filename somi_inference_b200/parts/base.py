@@ -23,8 +23,13 @@ Interfaces (duck-typed; the classes below only document them):
 * Embedding:     `forward(batch) -> Tensor` float32 [T, H]: the residual stream's start, from
                  `batch.token_ids` (and whatever else of the batch it needs: positions, ...).
 * Block arrangement: built as `cls(mixer, feed_forward, norms)` (`norms`: name -> norm; a
-                 part the layer does not have is None); `forward(residual, pending, batch,
-                 cache, owns_cache)` returns the delta that the next norm has to add.
+                 part the layer does not have is None), with a fourth argument `extras`
+                 (name -> built layer extra) where the layer has some; `forward(residual,
+                 pending, batch, cache, owns_cache)` returns the delta that the next norm has to
+                 add (a tensor, or a `GatedDelta` for norms that take one).  An arrangement
+                 whose extras keep state per request answers `state_needs() -> StateNeeds`.
+* Layer extra:   whatever its arrangement calls; `declare(params)` and `__init__(params,
+                 tensors, ctx)` like every part.
 """
 
 from __future__ import annotations
@@ -78,7 +83,8 @@ class PagedKVNeeds:
     num_kv_heads: int
     head_dim: int                 # width of a key
     window: int | None = None     # None: all keys; n: only the last n positions are ever read
-    value_dim: int | None = None  # width of a value; None: the same as a key's
+    value_dim: int | None = None  # width of a value; None: the same as a key's; 0: no values
+                                  # are stored (the keys are read as values too)
 
     @property
     def value_width(self) -> int:
@@ -96,6 +102,16 @@ class StateNeeds:
 class CacheNeeds:
     paged: PagedKVNeeds | None = None
     state: StateNeeds | None = None
+
+
+@dataclass
+class GatedDelta:
+    """What a gated residual branch hands to the next norm: the branch's result ([T, H], or
+    float32 [splits, T, H] partial sums) and the gate's logits [T, H] (rows may lie further
+    apart than H: a view into a wider product).  The norm adds sigmoid(logits) * delta."""
+
+    delta: torch.Tensor
+    gate_logits: torch.Tensor | None = None
 
 
 def names_of(params: Mapping[str, Any]) -> Mapping[str, str]:

@@ -9,6 +9,7 @@ while normalising, and returns its own feed-forward output as the next `pending`
 
 from __future__ import annotations
 
+from .base import GatedDelta, StateNeeds
 from .registry import ARRANGEMENTS
 
 
@@ -30,3 +31,54 @@ class PreNormBlock:
         a = self.mixer.forward(h, batch, cache, owns_cache)
         h = self.feed_forward_norm.forward(residual, a)
         return self.feed_forward.forward(h, batch)
+
+
+@ARRANGEMENTS.register("gated_pre_norm")
+class GatedPreNormBlock:
+    """Pre-norm with a gate on each branch and a short convolution in front of the mixer:
+        h = norm1(x);  x = x + sigmoid(G1 h) * mixer(h + conv(h))
+        h = norm2(x);  x = x + sigmoid(G2 h) * feed_forward(h)          (where the layer has one)
+    The gates read what the norm produced (before the convolution).  Extras: `mixer_gate`,
+    `mixer_taps` (either may be absent), `feed_forward_gate`.  The sums and the sigmoid are made
+    by the next norm's kernel, which gets the branch and the gate's logits as a `GatedDelta`."""
+
+    def __init__(self, mixer, feed_forward, norms, extras=None) -> None:
+        extras = dict(extras or {})
+        if mixer is None:
+            raise ValueError("the gated pre-norm arrangement needs a mixer")
+        want = {"mixer"} | ({"feed_forward"} if feed_forward is not None else set())
+        if set(norms) != want:
+            raise ValueError(f"the gated pre-norm arrangement takes the norms {sorted(want)}, "
+                             f"got {sorted(norms)}")
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = norms["mixer"]
+        self.feed_forward_norm = norms.get("feed_forward")
+        self.mixer_gate = extras.pop("mixer_gate", None)
+        self.mixer_taps = extras.pop("mixer_taps", None)
+        self.feed_forward_gate = extras.pop("feed_forward_gate", None)
+        if extras:
+            raise ValueError(f"the gated pre-norm arrangement has no use for {sorted(extras)}")
+        # the feed-forward's gate reads the same rows as its up projection: one product for both
+        self.fused_ff_gate = (self.feed_forward_gate is not None
+                              and hasattr(feed_forward, "attach_side"))
+        if self.fused_ff_gate:
+            feed_forward.attach_side(self.feed_forward_gate.weight, self.feed_forward_gate.bias)
+
+    def state_needs(self) -> StateNeeds:
+        return self.mixer_taps.state_needs() if self.mixer_taps is not None else StateNeeds({})
+
+    def forward(self, residual, pending, batch, cache, owns_cache):
+        h = self.mixer_norm.forward(residual, pending)
+        gate = self.mixer_gate.logits(h) if self.mixer_gate is not None else None
+        if self.mixer_taps is not None:
+            h = self.mixer_taps.forward(h, batch, cache.state)
+        pending = GatedDelta(self.mixer.forward(h, batch, cache, owns_cache), gate)
+        if self.feed_forward is None:
+            return pending
+        h = self.feed_forward_norm.forward(residual, pending)
+        if self.fused_ff_gate:
+            y, gate = self.feed_forward.forward(h, batch, side=True)
+            return GatedDelta(y, gate)
+        gate = self.feed_forward_gate.logits(h) if self.feed_forward_gate is not None else None
+        return GatedDelta(self.feed_forward.forward(h, batch), gate)

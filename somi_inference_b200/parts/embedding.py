@@ -12,7 +12,7 @@ import torch
 
 from .base import BuildContext, TensorDecl, names_of
 from .linear import Linear
-from .registry import EMBEDDINGS, HEADS
+from .registry import EMBEDDINGS, HEADS, NORMS
 
 
 @EMBEDDINGS.register("token_embedding")
@@ -32,6 +32,41 @@ class TokenEmbedding:
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32,
                           device=token_ids.device)
         self.ctx.ops.embed(token_ids, self.weight, out)
+        return out
+
+
+@EMBEDDINGS.register("sinusoid_embedding")
+class SinusoidEmbedding:
+    """x = norm(E[token] + s(position)): s has sin(p * base^(-2i/H)) at entry 2i and the cosine
+    of the same angle at entry 2i + 1; `norm` is a norm part (its weight is this part's).  The
+    frequencies are made once on the host (float64, rounded to float32); angles, sine, cosine
+    and the norm are float32 in the kernel, which writes the residual stream."""
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        return [TensorDecl(names_of(params)["weight"],
+                           (int(params["vocab_size"]), int(params["hidden_size"]))),
+                *NORMS.declare(params["norm"])]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        self.ctx = ctx
+        self.weight = tensors[names_of(params)["weight"]]
+        self.hidden = int(params["hidden_size"])
+        if self.hidden % 2:
+            raise ValueError("a sinusoid embedding needs an even width")
+        norm = params["norm"]
+        if norm.kind != "layernorm":
+            raise ValueError(f"the sinusoid embedding's kernel applies a layer norm, not {norm.kind!r}")
+        self.norm_weight = tensors[names_of(norm.params)["weight"]]
+        self.eps = float(norm.params["eps"])
+        i = torch.arange(0, self.hidden, 2, dtype=torch.float64)
+        self.inv_freq = (float(params["base"]) ** (-i / self.hidden)).to(torch.float32).to(ctx.device)
+
+    def forward(self, batch) -> torch.Tensor:
+        out = torch.empty((batch.token_ids.shape[0], self.hidden), dtype=torch.float32,
+                          device=batch.token_ids.device)
+        self.ctx.ops.embed_sinusoid_layernorm(batch.token_ids, batch.positions, self.weight,
+                                              self.inv_freq, self.norm_weight, self.eps, out)
         return out
 
 

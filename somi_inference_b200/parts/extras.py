@@ -1,0 +1,64 @@
+"""Layer extras: parts of a layer that are neither mixer, feed-forward nor norm.
+
+* `sigmoid_gate`: logits = W h + b; the branch it gates is multiplied by sigmoid(logits) when
+  the next norm adds it to the residual stream (the sigmoid and the product are float32, in the
+  norm's kernel).
+* `causal_taps`: h <- h + conv(h), a causal convolution over time on every channel,
+  conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) with zeros before a sequence's start.  The last
+  taps - 1 inputs of every request are kept in a state slot, so a sequence may arrive in portions
+  of any size.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, StateNeeds, TensorDecl, names_of
+from .linear import Linear
+from .registry import LAYER_EXTRAS
+
+
+@LAYER_EXTRAS.register("sigmoid_gate")
+class SigmoidGate:
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        n = names_of(params)
+        return [TensorDecl(n["weight"], (int(params["out_features"]), int(params["in_features"]))),
+                TensorDecl(n["bias"], (int(params["out_features"]),), init="zeros", matrix=False)]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        n = names_of(params)
+        self.weight = tensors[n["weight"]]
+        self.bias = tensors[n["bias"]].float()
+        self.proj = Linear(self.weight, self.bias, ctx.ops)
+
+    def logits(self, h: torch.Tensor) -> torch.Tensor:
+        return self.proj(h)
+
+
+@LAYER_EXTRAS.register("causal_taps")
+class CausalTaps:
+    STATE = "taps"
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        return [TensorDecl(names_of(params)["weight"], (int(params["channels"]), int(params["taps"])),
+                           matrix=False)]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        self.ctx = ctx
+        self.channels = int(params["channels"])
+        self.taps = int(params["taps"])
+        ctx.ops.check_taps(self.taps)
+        self.weight = tensors[names_of(params)["weight"]].float().contiguous()
+
+    def state_needs(self) -> StateNeeds:
+        """The last taps - 1 inputs of a request, oldest first, in the compute dtype."""
+        if self.taps == 1:
+            return StateNeeds({})
+        return StateNeeds({self.STATE: ((self.taps - 1, self.channels), self.ctx.dtype)})
+
+    def forward(self, h: torch.Tensor, batch, state: dict) -> torch.Tensor:
+        out = torch.empty_like(h)
+        self.ctx.ops.causal_taps(h, self.weight, state.get(self.STATE), batch, out)
+        return out

@@ -46,3 +46,61 @@ class SwiGLU:
             self.ctx.ops.silu_mul(gu, act, interleaved=True)
         partial = self.down.partial_sums(act)
         return partial if partial is not None else self.down(act)
+
+
+@FEED_FORWARDS.register("dense_ff")
+class DenseFF:
+    """y = W_down act(W_up h + b_up) + b_down with an activation that has parameters of its own.
+
+    `activation` "xielu": with (p, q) the two numbers of the tensor `act`,
+    act(z) = softplus(p) z^2 + z/2 for z > 0 and (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2
+    otherwise, evaluated in float32.  `forward(x, batch, side=...)` lets the caller ride a second
+    projection of the same input (a gate of the residual branch) on the up projection's product:
+    the side matrix's rows are appended to W_up's, and its output comes back as a view."""
+
+    graph_safe = True
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        n = names_of(params)
+        hidden, inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        decl = [TensorDecl(n["up"], (inter, hidden)), TensorDecl(n["down"], (hidden, inter)),
+                TensorDecl(n["act"], (2,), matrix=False)]
+        if params.get("bias"):
+            decl += [TensorDecl(n["up_bias"], (inter,), init="zeros", matrix=False),
+                     TensorDecl(n["down_bias"], (hidden,), init="zeros", matrix=False)]
+        return decl
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        n = names_of(params)
+        if params.get("activation") != "xielu":
+            raise ValueError(f"unknown activation {params.get('activation')!r} (known: 'xielu')")
+        self.ctx = ctx
+        self.inter = int(params["intermediate_size"])
+        bias = bool(params.get("bias"))
+        self.up_weight = tensors[n["up"]]
+        self.up_bias = tensors[n["up_bias"]].float() if bias else None
+        self.up = Linear(self.up_weight, self.up_bias, ctx.ops)
+        self.down = Linear(tensors[n["down"]], tensors[n["down_bias"]].float() if bias else None,
+                           ctx.ops)
+        self.act = tensors[n["act"]].float().contiguous()
+        self._with_side = None
+
+    def attach_side(self, weight: torch.Tensor, bias: torch.Tensor | None) -> None:
+        """Append a second projection of the same input to the up projection."""
+        w = torch.cat([self.up_weight, weight], 0).contiguous()
+        b = None
+        if self.up_bias is not None or bias is not None:
+            zeros = lambda k: torch.zeros(k, dtype=torch.float32, device=w.device)
+            b = torch.cat([self.up_bias if self.up_bias is not None else zeros(self.inter),
+                           bias.float() if bias is not None else zeros(weight.shape[0])], 0)
+        self._with_side = Linear(w, b, self.ctx.ops)
+
+    def forward(self, x: torch.Tensor, batch, side: bool = False):
+        proj = self._with_side if side else self.up
+        z = proj(x)                                     # [T, inter (+ side)]
+        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        self.ctx.ops.xielu(z, self.inter, self.act, act)
+        partial = self.down.partial_sums(act)
+        y = partial if partial is not None else self.down(act)
+        return (y, z[:, self.inter:]) if side else y

@@ -13,8 +13,9 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import LayerSpec, ModelSpec
-from .base import BuildContext, CacheNeeds, TensorDecl
-from .registry import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS)
+from .base import BuildContext, CacheNeeds, StateNeeds, TensorDecl
+from .registry import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, LAYER_EXTRAS, MIXERS,
+                       NORMS)
 
 
 def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
@@ -35,6 +36,8 @@ def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
             add(FEED_FORWARDS.declare(layer.feed_forward))
         for norm in layer.norms.values():
             add(NORMS.declare(norm))
+        for extra in layer.extras.values():
+            add(LAYER_EXTRAS.declare(extra))
     add(NORMS.declare(spec.final_norm))
     add(HEADS.declare(spec.head))
     return out
@@ -66,13 +69,29 @@ class Decoder:
         ff = (None if layer.feed_forward is None
               else FEED_FORWARDS.build(layer.feed_forward, placed, self.ctx))
         norms = {name: NORMS.build(spec, placed, self.ctx) for name, spec in layer.norms.items()}
-        return ARRANGEMENTS.get(layer.arrangement)(mixer, ff, norms)
+        if not layer.extras:
+            return ARRANGEMENTS.get(layer.arrangement)(mixer, ff, norms)
+        extras = {name: LAYER_EXTRAS.build(spec, placed, self.ctx)
+                  for name, spec in layer.extras.items()}
+        return ARRANGEMENTS.get(layer.arrangement)(mixer, ff, norms, extras)
 
     def cache_needs(self) -> tuple[list[CacheNeeds | None], list[int | None]]:
-        """Per run of the schedule: what its mixer needs (None: no mixer, or nothing), and
-        whose cache it reads."""
-        mixers = [self.layers[run.layer].mixer for run in self.schedule]
-        needs = [None if m is None else m.cache_needs() for m in mixers]
+        """Per run of the schedule: what its mixer needs (None: no mixer, or nothing) together
+        with the state that the layer's arrangement keeps for its extras, and whose cache the
+        run reads."""
+        needs: list[CacheNeeds | None] = []
+        for run in self.schedule:
+            block = self.layers[run.layer]
+            n = None if block.mixer is None else block.mixer.cache_needs()
+            extra = block.state_needs() if hasattr(block, "state_needs") else None
+            if extra is not None and extra.tensors:
+                paged = None if n is None else n.paged
+                own = {} if n is None or n.state is None else dict(n.state.tensors)
+                clash = set(own) & set(extra.tensors)
+                if clash:
+                    raise ValueError(f"state names used twice in one layer: {sorted(clash)}")
+                n = CacheNeeds(paged=paged, state=StateNeeds({**own, **extra.tensors}))
+            needs.append(n)
         owners = [run.cache_of for run in self.schedule]
         return needs, owners
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildContext, TensorDecl, names_of
+from .base import BuildContext, GatedDelta, TensorDecl, names_of
 from .registry import NORMS
 
 
@@ -33,4 +33,32 @@ class RMSNorm:
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=residual.device)
         self.ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
+        return out
+
+
+@NORMS.register("layernorm")
+class LayerNorm:
+    """(x - mean) / sqrt(var + eps) * weight, var the mean of the squared deviations; a weight and
+    no bias.  Mean, variance and the residual sum are float32.  `delta` may be a `GatedDelta`:
+    the branch's result is then multiplied by sigmoid(gate logits) as it is added."""
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        return [TensorDecl(names_of(params)["weight"], (int(params["size"]),), init="ones",
+                           matrix=False)]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.ctx = ctx
+        self.weight = tensors[names_of(params)["weight"]]
+
+    def forward(self, residual: torch.Tensor, delta=None,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+        gate = None
+        if isinstance(delta, GatedDelta):
+            delta, gate = delta.delta, delta.gate_logits
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=residual.device)
+        self.ctx.ops.add_layernorm(residual, delta, gate, self.weight, self.eps, out, rows)
         return out

@@ -55,3 +55,4 @@ POSITION_ENCODINGS = PartRegistry("position encoding")
 EMBEDDINGS = PartRegistry("embedding")
 HEADS = PartRegistry("head")
 ARRANGEMENTS = PartRegistry("block arrangement")
+LAYER_EXTRAS = PartRegistry("layer extra")

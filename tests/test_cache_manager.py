@@ -116,12 +116,30 @@ def test_state_slots_are_zeroed_and_reused():
     assert m.view(0).state["h"].data_ptr() != m.view(1).state["h"].data_ptr()
 
 
-def test_reader_runs_share_the_owners_view():
+def test_reader_runs_share_the_owners_pages():
     needs = [CacheNeeds(paged=PagedKVNeeds(2, 8, None))] * 3
     m = CacheManager(needs, [None, None, 0], num_pages=4, page_size=4, max_requests=2,
                      max_positions=16, dtype=torch.float32, device="cpu")
-    assert m.view(2) is m.view(0)
+    assert m.view(2).paged is m.view(0).paged
     assert m.groups[0].storage.shape[0] == 2    # the reader owns no storage
+
+
+def test_reader_runs_keep_state_of_their_own():
+    from somi_inference_b200.parts.base import StateNeeds
+    state = StateNeeds({"tail": ((3, 5), torch.float32)})
+    needs = [CacheNeeds(paged=PagedKVNeeds(1, 8, 6, value_dim=0), state=state)] * 2
+    m = CacheManager(needs, [None, 0], num_pages=4, page_size=4, max_requests=2,
+                     max_positions=64, dtype=torch.float32, device="cpu")
+    assert m.view(1).paged is m.view(0).paged
+    assert m.view(0).paged.values is None and m.view(0).paged.keys.shape == (4, 1, 4, 8)
+    a, b = m.view(0).state["tail"], m.view(1).state["tail"]
+    assert a.shape == b.shape == (2, 3, 5) and a.data_ptr() != b.data_ptr()
+    s = m.register("r")
+    a[s] = 1.0
+    b[s] = 2.0
+    m.release("r")
+    assert m.register("again") == s             # the slot is used again, both tensors zeroed
+    assert float(a[s].abs().sum()) == 0.0 and float(b[s].abs().sum()) == 0.0
 
 
 @pytest.mark.parametrize("seed", range(6))
