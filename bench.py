@@ -4,6 +4,7 @@
     python bench.py --impl reference [--steps K] [--warmup W]    luke396/somi-inference, same step
     python bench.py --only decode|prefill|mixed [--shape 0.5b|7b|14b] [--layers L] [--batch B]
                     [--context C] [--prefill-tokens T] [--profile]      one phase (profiling runs)
+    python bench.py --arch digosun --only decode|prefill [...]   the same shapes with Digosun layers
 
 A step is one decode step of the whole engine: 8 requests with 2,048 cached tokens each,
 random bfloat16 weights, one new token per request (batch layout upload, all layers, head,
@@ -44,6 +45,17 @@ SHAPES = {
                 rope_theta=1e6, rms_norm_eps=1e-5, tie_word_embeddings=False),
 }
 FULL_LAYERS = {k: v["num_hidden_layers"] for k, v in SHAPES.items()}
+# `--arch digosun`: the same widths, head counts, head sizes, feed-forward sizes, layer counts
+# and vocabularies with the Digosun layer (latent attention under a sliding window, every second
+# layer reading the latent of the layer before it, gated branches, four taps).  The latents are
+# as wide as models of this kind make them: a key/value latent of a kv head pair's width or
+# wider, a query latent of about 0.4 widths.
+DIGOSUN_SHAPES = {
+    "0.5b": dict(q_rank=384, kv_rank=128, window=1024),
+    "7b": dict(q_rank=1536, kv_rank=512, window=1024),
+    "14b": dict(q_rank=1536, kv_rank=512, window=1024),
+}
+DIGOSUN_TAPS = 4
 CONTEXT = 2048          # cached tokens per request when decode is timed
 MAX_CONTEXT = 4096      # "benchmark at context 4096": positions the model is laid out for
 LONG_CONTEXT = 40960    # ... when the points at 8 k and 32 k cached tokens are measured too
@@ -183,13 +195,33 @@ def config_record(shape: str, layers: int, batch: int, positions: int) -> dict:
             "l2": "no flush: a step reads more than the 126 MB L2"}
 
 
+def digosun_config(shape: str, layers: int, positions: int) -> dict:
+    q, d = SHAPES[shape], DIGOSUN_SHAPES[shape]
+    mixer = dict(heads=q["num_attention_heads"], dim=q["head_dim"], vdim=q["head_dim"],
+                 q_rank=d["q_rank"], kv_rank=d["kv_rank"], scale=q["head_dim"] ** -0.5,
+                 mask={"size": d["window"]})
+    mlp = {"kind": "dense", "ff": q["intermediate_size"]}
+    return {"architecture": "Digosun", "vocab": q["vocab_size"], "width": q["hidden_size"],
+            "norm": {"eps": q["rms_norm_eps"]}, "canon": {"taps": DIGOSUN_TAPS},
+            "max_positions": positions,
+            "layers": [{"type": "latent_attention", "mlp": mlp,
+                        "mixer": dict(mixer, **({"kv_from": i - 1} if i % 2 else {}))}
+                       for i in range(layers)]}
+
+
+ARCH = "qwen2"     # set by --arch; "digosun" builds the same shapes with the Digosun layer
+
+
 def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, positions: int):
     import torch
 
-    from somi_inference_b200.config import Qwen2Config
+    from somi_inference_b200.config import DigosunConfig, Qwen2Config
     from somi_inference_b200.engine import Engine
     from somi_inference_b200.parts import declared_tensors
-    cfg = Qwen2Config.from_dict(shape_config(shape, layers, positions))
+    if ARCH == "digosun":
+        cfg = DigosunConfig.from_dict(digosun_config(shape, layers, positions))
+    else:
+        cfg = Qwen2Config.from_dict(shape_config(shape, layers, positions))
     gen = torch.Generator(device="cuda").manual_seed(0)
     tensors = {}
     for name, d in declared_tensors(cfg.to_model_spec()).items():
@@ -206,7 +238,31 @@ def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, po
     return cfg, eng
 
 
+def digosun_sizes(cfg) -> dict:
+    """The same figures for a Digosun model: weights a decode step reads once, cached bytes per
+    position (the latent, once per layer that keeps one), matrix parameters, and attention flops
+    per (query, key) pair in the form the engine computes it (scores and sums over the latent)."""
+    D, V = cfg.width, cfg.vocab
+    params = kv = pair = small = 0
+    for layer in cfg.layers:
+        m = layer.mixer
+        own = m.kv_from is None
+        params += (m.q_rank + (m.kv_rank if own else 0)) * D + m.heads * m.dim * m.q_rank
+        params += m.heads * (m.dim + m.vdim) * m.kv_rank + D * m.heads * m.vdim + D * D
+        small += m.q_rank + (m.kv_rank if own else 0) + m.heads + 2 * D + cfg.taps * D
+        if layer.ff is not None:
+            params += 2 * D * layer.ff + D * D
+            small += layer.ff + 3 * D + 2
+        kv += 2 * m.kv_rank if own else 0
+        pair += 4 * m.heads * m.kv_rank
+    return {"weight_bytes": 2 * (params + small + V * D + 2 * D), "kv_bytes_per_token": kv,
+            "matmul_params": params, "head_params": V * D, "attn_flops_per_pair": pair,
+            "window": min((l.mixer.window or 1 << 30) for l in cfg.layers)}
+
+
 def model_sizes(cfg, layers: int) -> dict:
+    if ARCH == "digosun":
+        return digosun_sizes(cfg)
     H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     nq, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     per_layer = (nq + 2 * nkv) * hd * H + (nq + 2 * nkv) * hd + nq * hd * H + 3 * H * I + 2 * H
@@ -271,7 +327,9 @@ def time_decode(eng, sampler, reqs, vocab: int, steps: int, warmup: int):
 
 
 def decode_roofline(sizes: dict, batch: int, context_mid: float, ms: float, pk: dict, kind: str) -> dict:
-    step_bytes = sizes["weight_bytes"] + batch * context_mid * sizes["kv_bytes_per_token"]
+    # (a sliding window bounds what a step reads of a request's cache)
+    step_bytes = sizes["weight_bytes"] + batch * min(context_mid, sizes.get("window", 1 << 30)) \
+        * sizes["kv_bytes_per_token"]
     achieved = step_bytes / (ms * 1e-3) / 1e9
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
             "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": kind}
@@ -303,7 +361,9 @@ def time_prefill(eng, vocab: int, n_tokens: int, sizes: dict, pk: dict, reps: in
         times.append(s.elapsed_time(e))
     tail = sorted(times[2:])
     ms = tail[len(tail) // 2]
-    flops = step_flops(sizes, n_tokens, 1, n_tokens * (n_tokens + 1) // 2)
+    w = min(sizes.get("window", n_tokens), n_tokens)
+    pairs = w * (w + 1) // 2 + (n_tokens - w) * w          # every query sees at most w keys
+    flops = step_flops(sizes, n_tokens, 1, pairs)
     return {"value": round(n_tokens / ms * 1e3, 1), "tokens": n_tokens, "ms": round(ms, 3),
             "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
@@ -513,7 +573,7 @@ def run_only(args, pk: dict, kind: str) -> int:
         sampler = Sampler(eng.ops, eng.device)
         reqs = fill_context(eng, args.batch, cfg.vocab_size, "main", args.context)
         ms, launches, per_step = time_decode(eng, sampler, reqs, cfg.vocab_size, args.steps, args.warmup)
-        line = {"only": "decode", "shape": shape, "layers": layers, "batch": args.batch,
+        line = {"only": "decode", "arch": ARCH, "shape": shape, "layers": layers, "batch": args.batch,
                 "context": args.context, "ms_per_step": round(ms, 4),
                 "tokens_per_s": round(args.batch / ms * 1e3, 1), "gpu_launches": int(launches),
                 "latency": latency_stats(per_step),
@@ -531,7 +591,7 @@ def run_only(args, pk: dict, kind: str) -> int:
         n = args.prefill_tokens
         cfg, eng = build_engine(shape, layers, n + 64, 2, max(MAX_CONTEXT, n))
         sizes = model_sizes(cfg, layers)
-        line = {"only": "prefill", "shape": shape, "layers": layers,
+        line = {"only": "prefill", "arch": ARCH, "shape": shape, "layers": layers,
                 **time_prefill(eng, cfg.vocab_size, n, sizes, pk)}
         if args.profile:
             g = torch.Generator().manual_seed(6)
@@ -794,6 +854,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--shape", choices=list(SHAPES), default="7b")
+    ap.add_argument("--arch", choices=["qwen2", "digosun"], default="qwen2",
+                    help="with --only decode|prefill: the layer design the shape is built with "
+                         "(digosun: latent attention under a window, gated branches)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true",
@@ -822,6 +885,12 @@ def main() -> int:
         print("bench.py: --context and --prefill-tokens go with --only decode / --only prefill")
         return 2
     pk, kind = peaks()
+    if args.arch != "qwen2":
+        if args.only not in ("decode", "prefill"):
+            print("bench.py: --arch digosun goes with --only decode or --only prefill")
+            return 2
+        global ARCH
+        ARCH = args.arch
     if args.only is not None:
         return run_only(args, pk, kind)
 

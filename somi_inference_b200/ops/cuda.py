@@ -71,6 +71,8 @@ class CudaOps:
             self.generic_q_tile, self.prefill_q_tile, self.prefill_tc_q_tile,
             self.prefill_pp_q_tile, self.latent_q_tile)))
         self.max_taps = int(self.lib.somi_causal_taps_max())
+        self.use_mma_latent = True
+        assert int(self.lib.somi_latent_attention_mma_q_tile()) == self.latent_q_tile
         self.use_pp_prefill = True
         self.pp_prefill_min_ctas = torch.cuda.get_device_properties(0).multi_processor_count
         self.use_tc_prefill = True
@@ -580,6 +582,33 @@ class CudaOps:
         T = q.shape[1]
         tiles = batch.tiles[self.latent_q_tile]
         n_decode = batch.num_requests - batch.num_prefill_requests
+        win = int(window) if window else 0
+        if (self.use_mma_latent and q.dtype == torch.bfloat16
+                and bool(self.lib.somi_latent_attention_mma_supported(ctypes.c_int(heads),
+                                                                      ctypes.c_int(rank)))):
+            # tensor cores: 16 tokens x 4 heads per CTA for prompt portions; all heads of a
+            # single-token request per CTA, its keys in chunks whose partial sums are merged
+            max_kv = group.width * page_size      # a bound that changes with the layout only
+            splits = int(self.lib.somi_latent_attention_mma_splits(ctypes.c_int(max_kv),
+                                                                   ctypes.c_int(win)))
+            ws = self._scratch(n_decode * heads * splits * (rank + 2), q.device) if splits > 1 and n_decode else None
+            rc = self.lib.somi_latent_attention_mma(
+                _ptr(q), ctypes.c_longlong(rank), ctypes.c_longlong(T * rank), _ptr(cache),
+                _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+                ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
+                ctypes.c_int(n_decode), ctypes.c_int(max_kv), ctypes.c_int(heads),
+                ctypes.c_int(rank), ctypes.c_int(page_size), ctypes.c_float(scale),
+                ctypes.c_int(win), _ptr(sinks), _ptr(out), ctypes.c_longlong(rank),
+                ctypes.c_longlong(T * rank), _ptr(ws), self._stream())
+            self._done(rc, "latent_attention_mma")
+            self.launches += (1 if tiles.shape[0] and n_decode else 0) + (1 if splits > 1 and n_decode else 0)
+            if trace.active():
+                moved, flops = self._attention_work(batch, 0, batch.num_requests, heads, 1, rank,
+                                                    q.element_size(), win)
+                trace.note("latent_attention_mma", moved / 2 + heads * T * rank * q.element_size(), flops,
+                           detail=f"splits={splits}" if n_decode else "")
+            return
         rc = self.lib.somi_latent_attention_generic(
             _ptr(q), _code(q), ctypes.c_longlong(rank), ctypes.c_longlong(T * rank), _ptr(cache),
             _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),

@@ -210,7 +210,7 @@ def test_head_products(ops, dtype, T):
 
 # ------------------------------------------------------------------ attention over the latent cache
 def run_latent_attention(ops, requests, *, heads, rank, window, page_size, dtype, sinks, plant=None,
-                         seed=0, scale=0.3):
+                         seed=0, scale=0.3, mma=True):
     """Fill the cache with the latents of whole sequences, run the kernel on the step's rows and
     compare with the plain attention over the same sequences (key = value = latent for every
     head).  `plant(seqs, queries)` may scale latents and queries before they are stored."""
@@ -233,9 +233,14 @@ def run_latent_attention(ops, requests, *, heads, rank, window, page_size, dtype
                 flat[page * page_size + p % page_size] = seqs[i][p].cuda()
     rows = torch.cat([queries[i][requests[i][0]:] for i in order])          # [T, H, R]
     q_dev = rows.transpose(0, 1).contiguous().cuda()                        # [H, T, R]
-    out = torch.empty_like(q_dev)
-    ops.latent_attention(q_dev, cache, batch, batch.groups[0], heads, rank, scale, window,
-                         None if sinks is None else sinks.cuda(), out)
+    out = torch.full_like(q_dev, float("nan"))
+    was = ops.use_mma_latent
+    ops.use_mma_latent = mma          # bfloat16: the tensor-core kernel, or the one on the CUDA cores
+    try:
+        ops.latent_attention(q_dev, cache, batch, batch.groups[0], heads, rank, scale, window,
+                             None if sinks is None else sinks.cuda(), out)
+    finally:
+        ops.use_mma_latent = was
     got = out.transpose(0, 1).double().cpu()
     sink = sinks.double() if sinks is not None else torch.full((heads,), -1e30, dtype=torch.float64)
     at = 0
@@ -249,23 +254,42 @@ def run_latent_attention(ops, requests, *, heads, rank, window, page_size, dtype
     return worst
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rank, heads, page_size", [(40, 3, 8), (64, 6, 16), (24, 1, 4), (136, 2, 16)])
-def test_latent_attention_random(ops, dtype, rank, heads, page_size):
+@pytest.mark.parametrize("dtype, mma", [(torch.float32, False), (torch.bfloat16, False),
+                                        (torch.bfloat16, True)])
+@pytest.mark.parametrize("rank, heads, page_size", [(40, 3, 8), (64, 6, 16), (24, 1, 4), (136, 2, 16),
+                                                    (36, 5, 16)])
+def test_latent_attention_random(ops, dtype, mma, rank, heads, page_size):
     sinks = torch.tensor([0.5, -2.0, 3.0, 0.0, 1.0, -1.0])[:heads]
     for window in (None, 1, 7, 33):
         reqs = [(0, 50), (37, 1), (3, 20), (0, 1), (64, 17), (31, 2), (90, 1)]
         err = run_latent_attention(ops, reqs, heads=heads, rank=rank, window=window,
-                                   page_size=page_size, dtype=dtype, sinks=sinks, seed=rank)
+                                   page_size=page_size, dtype=dtype, sinks=sinks, seed=rank, mma=mma)
         assert err < tol(dtype, 2e-5, 3e-2), (window, err)
     err = run_latent_attention(ops, [(0, 40), (20, 1)], heads=heads, rank=rank, window=9,
-                               page_size=page_size, dtype=dtype, sinks=None)
+                               page_size=page_size, dtype=dtype, sinks=None, mma=mma)
     assert err < tol(dtype, 2e-5, 3e-2)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rank, heads", [(512, 5), (264, 70), (128, 66), (64, 130)])
+def test_latent_attention_wide_and_many_heads(ops, rank, heads):
+    """The tensor-core kernel at its widest latent (output columns split over two warps), with
+    more heads than one CTA of a single-token request holds, and with single-token requests
+    whose keys span several chunks (with a window, and without one over a long context)."""
+    sinks = torch.linspace(-2, 2, heads)
+    reqs = [(0, 37), (700, 1), (255, 1), (256, 1), (40, 19), (1023, 1), (0, 1)]
+    for window in (None, 300, 257, 64):
+        err = run_latent_attention(ops, reqs, heads=heads, rank=rank, window=window, page_size=16,
+                                   dtype=torch.bfloat16, sinks=sinks, seed=rank, scale=0.12)
+        assert err < 3e-2, (window, err)
+    err = run_latent_attention(ops, reqs, heads=heads, rank=rank, window=None, page_size=16,
+                               dtype=torch.bfloat16, sinks=None, seed=1, scale=0.12)
+    assert err < 3e-2
+
+
+@pytest.mark.parametrize("dtype, mma", [(torch.float32, False), (torch.bfloat16, False),
+                                        (torch.bfloat16, True)])
 @pytest.mark.parametrize("decode", [False, True])
-def test_planted_key_far_back_and_at_window_edges(ops, dtype, decode):
+def test_planted_key_far_back_and_at_window_edges(ops, dtype, mma, decode):
     """One key gets a score far above the rest.  Without a window it lies hundreds of positions
     back; with a window of W it lies exactly W - 1 back (the last key seen) and exactly W back
     (the first key not seen), with the edge on and beside page borders."""
@@ -285,12 +309,13 @@ def test_planted_key_far_back_and_at_window_edges(ops, dtype, decode):
     reqs = [(last, 1)] if decode else [(total - 100, 100)]
     # far back, no window: the planted key carries (nearly) the whole output
     err = run_latent_attention(ops, reqs, heads=heads, rank=rank, window=None, page_size=ps,
-                               dtype=dtype, sinks=sinks, plant=planter(last, 3))
+                               dtype=dtype, sinks=sinks, plant=planter(last, 3), mma=mma)
     assert err < tol(dtype, 2e-5, 5e-2)
-    for W in (16, 17, 40, 48, 49, 129):
+    for W in (16, 17, 40, 48, 49, 129, 256, 321):
         for back in (W - 1, W):            # just inside, just outside
             err = run_latent_attention(ops, reqs, heads=heads, rank=rank, window=W, page_size=ps,
-                                       dtype=dtype, sinks=sinks, plant=planter(last, last - back))
+                                       dtype=dtype, sinks=sinks, plant=planter(last, last - back),
+                                       mma=mma)
             assert err < tol(dtype, 2e-5, 5e-2), (W, back, err)
 
 
