@@ -10,7 +10,8 @@
 // The sink adds to the denominator only: a key whose score is sink_h and whose value is zero.
 //
 // This file holds the kernel on the CUDA cores for any dtype and any latent width up to 512 (the
-// float32 path's kernel, and the bfloat16 path's for widths the tensor-core kernel refuses).
+// float32 path's kernel, and the bfloat16 path's for widths the tensor-core kernel of
+// attention_latent_mma.cu refuses).
 // Key tiles are aligned to multiples of kBN from position 0 and the softmax is online in
 // float32, so a row's arithmetic does not depend on how its request was cut into steps.
 //
@@ -135,6 +136,7 @@ latent_attention_generic_kernel(const T* __restrict__ q, long long q_tok_stride,
                 const int m = idx / R, d = idx - m * R;
                 float o = acc[i] * a_s[m];
                 const float* p = Ss + m * (kLBN + 1);
+#pragma unroll 4
                 for (int n = 0; n < kLBN; ++n) o = fmaf(p[n], Cs[n * Rp + d], o);
                 acc[i] = o;
             }
@@ -187,370 +189,5 @@ SOMI_API int somi_latent_attention_generic(
     if (dtype == SOMI_F32) SOMI_LAUNCH_LATT(float);
     else SOMI_LAUNCH_LATT(__nv_bfloat16);
 #undef SOMI_LAUNCH_LATT
-    return launch_status();
-}
-
-// ====================================================================== tensor cores
-// The bfloat16 kernel: the same attention on m16n8k16 tensor-core instructions.
-//
-// A CTA owns 64 rows, a row being one (token, head) pair; all rows of a CTA read the same
-// latent tiles, which is what makes the shared latent pay: a tile of 64 cached positions is
-// fetched once (asynchronous 16-byte copies, page by page, into double-buffered swizzled shared
-// memory) and serves as the keys of S = Q' C^T and, read transposed, as the values of O += P C.
-//   * prompt portions: 16 consecutive tokens of a request x 4 heads (`tokb` = 16); the four
-//     16-row MMA tiles are the four heads;
-//   * single-token requests: 1 token x 64 heads (`tokb` = 1), and the request's keys are cut into
-//     chunks of `chunk` positions, one CTA (blockIdx.z) each, whose partial sums (float32, with
-//     their maximum and denominator) a merge kernel adds up; with one chunk the CTA writes the
-//     result itself.
-// RT is the latent width rounded up to 64/128/256/512 (columns beyond the width are zeros in
-// shared memory).  Up to RT = 256 a warp owns 16 rows and all columns of O (four warps); at
-// RT = 512 the output columns are split over two warps that both compute their rows' scores
-// (eight warps: registers hold 16 x 256 accumulators at most).  Softmax: online, float32,
-// base 2; the sink enters as the starting maximum with denominator 1 (or in the merge).
-#include "mma.cuh"
-
-namespace somi {
-
-constexpr int kLtRows = 64;
-constexpr int kLtBN = 64;
-
-template <int RT>
-__device__ __forceinline__ void load_latent_tile(unsigned char* dst,
-                                                 const __nv_bfloat16* __restrict__ cache,
-                                                 const int* __restrict__ bt, int kb, int k_lo,
-                                                 int k_hi, int R, int page_size, int tid,
-                                                 int threads) {
-    constexpr int CPR = RT / 8;
-    for (int c = tid; c < kLtBN * CPR; c += threads) {
-        const int r = c / CPR, ch = c - r * CPR;
-        const int j = kb + r;
-        const bool ok = j >= k_lo && j < k_hi && ch * 8 < R;
-        size_t off = 0;
-        if (ok) {
-            const int page = bt[j / page_size];
-            off = (static_cast<size_t>(page) * page_size + j % page_size) * R + ch * 8;
-        }
-        cp_async_16(smem_u32(dst + swizzled_offset<RT>(r, ch)), cache + off, ok ? 16 : 0);
-    }
-}
-
-template <int RT, int CSPLIT>
-__global__ void __launch_bounds__(128 * CSPLIT)
-latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok_stride,
-                            long long q_head_stride, const __nv_bfloat16* __restrict__ cache,
-                            const int* __restrict__ block_table, int bt_stride,
-                            const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
-                            const int* __restrict__ tiles, int req_base, int row_base, int tokb,
-                            int H, int R, int page_size, float scale_log2e, int window,
-                            const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
-                            long long o_tok_stride, long long o_head_stride, int chunk,
-                            float* __restrict__ part_o, float* __restrict__ part_ml,
-                            int max_splits) {
-    constexpr int CPR = RT / 8;
-    constexpr int TILE = kLtBN * RT * 2;
-    constexpr int THREADS = 128 * CSPLIT;
-    constexpr int OC = RT / 8 / CSPLIT;                 // 8-column output tiles per warp
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    unsigned char* Qs = smem_raw;                        // [64][RT]
-    unsigned char* Cs = Qs + kLtRows * RT * 2;           // 2 x [64][RT]
-    pdl_launch_dependents();
-    pdl_wait();
-
-    int req, row0, rows;
-    if (tiles) {
-        const int tile = gridDim.x - 1 - blockIdx.x;     // later tiles see more keys: first
-        req = tiles[3 * tile];
-        row0 = tiles[3 * tile + 1];
-        rows = tiles[3 * tile + 2];
-    } else {
-        req = req_base + blockIdx.x;
-        row0 = row_base + blockIdx.x;
-        rows = 1;
-    }
-    const int hb = kLtRows / tokb;                       // heads per CTA
-    const int head0 = blockIdx.y * hb;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int mt = warp & 3, cs = warp >> 2;
-    const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
-    const int kv_end = q_pos0 + rows;
-    const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
-    const int kb_first = (kv_first / kLtBN) * kLtBN;
-    // this CTA's share of the keys: chunk blockIdx.z, counted from the first key tile
-    int k_lo = kv_first, k_hi = kv_end, kb0 = kb_first;
-    if (chunk > 0) {
-        kb0 = kb_first + blockIdx.z * chunk;
-        k_lo = max(kv_first, kb0);
-        k_hi = min(kv_end, kb0 + chunk);
-    }
-    const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
-    const int n_tiles = k_hi > kb0 ? (k_hi - kb0 + kLtBN - 1) / kLtBN : 0;
-
-    for (int c = tid; c < kLtRows * CPR; c += THREADS) {
-        const int r = c / CPR, ch = c - r * CPR;
-        const int tok = r % tokb, head = head0 + r / tokb;
-        const bool ok = tok < rows && head < H && ch * 8 < R;
-        const __nv_bfloat16* src = q;
-        if (ok) src = q + static_cast<size_t>(row0 + tok) * q_tok_stride +
-                      static_cast<size_t>(head) * q_head_stride + ch * 8;
-        cp_async_16(smem_u32(Qs + swizzled_offset<RT>(r, ch)), src, ok ? 16 : 0);
-    }
-    if (n_tiles > 0) load_latent_tile<RT>(Cs, cache, bt, kb0, k_lo, k_hi, R, page_size, tid, THREADS);
-    cp_async_commit();
-
-    float o[OC][4];
-#pragma unroll
-    for (int a = 0; a < OC; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) o[a][b] = 0.f;
-    const int qr = mt * 16;
-    const int row_lo = qr + (lane >> 2), row_hi = row_lo + 8;
-    const int head_lo = head0 + row_lo / tokb, head_hi = head0 + row_hi / tokb;
-    const int pos_lo = q_pos0 + row_lo % tokb, pos_hi = q_pos0 + row_hi % tokb;
-    const bool ok_lo = row_lo % tokb < rows && head_lo < H, ok_hi = row_hi % tokb < rows && head_hi < H;
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-    if (sinks && chunk == 0) {
-        // the sink: a key of score sinks[head] without a value, counted once
-        if (ok_lo) { m_lo = sinks[head_lo] * 1.4426950408889634f; l_lo = 1.f; }
-        if (ok_hi) { m_hi = sinks[head_hi] * 1.4426950408889634f; l_hi = 1.f; }
-    }
-    const bool warp_live = head0 + qr / tokb < H;        // any row of this warp's tile is a head
-
-    for (int t = 0; t < n_tiles; ++t) {
-        const int kb = kb0 + t * kLtBN;
-        const int buf = t & 1;
-        if (t + 1 < n_tiles)
-            load_latent_tile<RT>(Cs + (buf ^ 1) * TILE, cache, bt, kb + kLtBN, k_lo, k_hi, R,
-                                 page_size, tid, THREADS);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        const unsigned char* Ct = Cs + buf * TILE;
-        if (warp_live) {
-            float s[8][4];
-#pragma unroll
-            for (int a = 0; a < 8; ++a)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
-#pragma unroll 4
-            for (int ks = 0; ks < RT / 16; ++ks) {
-                uint32_t a[4];
-                ldmatrix_x4(a, smem_u32(Qs + swizzled_offset<RT>(qr + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                                                2 * ks + (lane >> 4))));
-#pragma unroll
-                for (int np = 0; np < 4; ++np) {
-                    uint32_t b[4];
-                    ldmatrix_x4(b, smem_u32(Ct + swizzled_offset<RT>(np * 16 + (lane & 7) + (lane >> 4) * 8,
-                                                                    2 * ks + ((lane >> 3) & 1))));
-                    mma_bf16_16816(s[2 * np], a, b[0], b[1]);
-                    mma_bf16_16816(s[2 * np + 1], a, b[2], b[3]);
-                }
-            }
-            float t_lo = -INFINITY, t_hi = -INFINITY;
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = kb + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const int pos = e < 2 ? pos_lo : pos_hi;
-                    const bool ok = key <= pos && key >= k_lo && key < k_hi &&
-                                    (window <= 0 || key > pos - window);
-                    const float v = ok ? s[nt][e] * scale_log2e : -INFINITY;
-                    s[nt][e] = v;
-                    if (e < 2) t_lo = fmaxf(t_lo, v); else t_hi = fmaxf(t_hi, v);
-                }
-            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 1));
-            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
-            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1));
-            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
-            const float n_lo = fmaxf(m_lo, t_lo), n_hi = fmaxf(m_hi, t_hi);
-            const float b_lo = n_lo == -INFINITY ? 0.f : n_lo, b_hi = n_hi == -INFINITY ? 0.f : n_hi;
-            const float a_lo = exp2f(m_lo - b_lo), a_hi = exp2f(m_hi - b_hi);
-            m_lo = n_lo;
-            m_hi = n_hi;
-            float r_lo = 0.f, r_hi = 0.f;
-            uint32_t pa[4][4];
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const uint32_t lo = pack_bf16(exp2f(s[nt][0] - b_lo), exp2f(s[nt][1] - b_lo));
-                const uint32_t hi = pack_bf16(exp2f(s[nt][2] - b_hi), exp2f(s[nt][3] - b_hi));
-                const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&lo);
-                const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&hi);
-                r_lo += __low2float(lo2) + __high2float(lo2);
-                r_hi += __low2float(hi2) + __high2float(hi2);
-                pa[nt >> 1][(nt & 1) * 2] = lo;
-                pa[nt >> 1][(nt & 1) * 2 + 1] = hi;
-            }
-            r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 1);
-            r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 2);
-            r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 1);
-            r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 2);
-            l_lo = l_lo * a_lo + r_lo;
-            l_hi = l_hi * a_hi + r_hi;
-#pragma unroll
-            for (int nt = 0; nt < OC; ++nt) {
-                o[nt][0] *= a_lo; o[nt][1] *= a_lo;
-                o[nt][2] *= a_hi; o[nt][3] *= a_hi;
-            }
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-                for (int dc = 0; dc < OC / 2; ++dc) {
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, smem_u32(Ct + swizzled_offset<RT>(
-                                             kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                             2 * (cs * (OC / 2) + dc) + (lane >> 4))));
-                    mma_bf16_16816(o[2 * dc], pa[kk], b[0], b[1]);
-                    mma_bf16_16816(o[2 * dc + 1], pa[kk], b[2], b[3]);
-                }
-        }
-        __syncthreads();
-    }
-    cp_async_wait<0>();
-
-    if (chunk == 0) {
-        const float i_lo = l_lo > 0.f ? 1.0f / l_lo : 0.f, i_hi = l_hi > 0.f ? 1.0f / l_hi : 0.f;
-#pragma unroll
-        for (int nt = 0; nt < OC; ++nt) {
-            const int d = (cs * OC + nt) * 8 + (lane & 3) * 2;
-            if (d >= R) continue;
-            if (ok_lo)
-                *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + row_lo % tokb) * o_tok_stride +
-                                             static_cast<size_t>(head_lo) * o_head_stride + d) =
-                    pack_bf16(o[nt][0] * i_lo, o[nt][1] * i_lo);
-            if (ok_hi)
-                *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + row_hi % tokb) * o_tok_stride +
-                                             static_cast<size_t>(head_hi) * o_head_stride + d) =
-                    pack_bf16(o[nt][2] * i_hi, o[nt][3] * i_hi);
-        }
-        return;
-    }
-    // partial sums of this chunk (tokb == 1: the row is the head), unnormalised
-    const int i = blockIdx.x;
-    const size_t p_lo = (static_cast<size_t>(i) * H + head_lo) * max_splits + blockIdx.z;
-    const size_t p_hi = (static_cast<size_t>(i) * H + head_hi) * max_splits + blockIdx.z;
-#pragma unroll
-    for (int nt = 0; nt < OC; ++nt) {
-        const int d = (cs * OC + nt) * 8 + (lane & 3) * 2;
-        if (d >= R) continue;
-        if (ok_lo) *reinterpret_cast<float2*>(part_o + p_lo * R + d) = make_float2(o[nt][0], o[nt][1]);
-        if (ok_hi) *reinterpret_cast<float2*>(part_o + p_hi * R + d) = make_float2(o[nt][2], o[nt][3]);
-    }
-    if (cs == 0 && (lane & 3) == 0) {
-        if (ok_lo) *reinterpret_cast<float2*>(part_ml + 2 * p_lo) = make_float2(m_lo, l_lo);
-        if (ok_hi) *reinterpret_cast<float2*>(part_ml + 2 * p_hi) = make_float2(m_hi, l_hi);
-    }
-}
-
-// out[h][row] = sum_s 2^(m_s - M) o_s / (sum_s 2^(m_s - M) l_s + 2^(sink_h log2 e - M)) over the
-// chunks that held keys; M is the maximum over the chunks and the sink.
-__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    int max_splits, int n_splits, int H, int R,
-                                    const float* __restrict__ sinks, int row_base,
-                                    __nv_bfloat16* __restrict__ out, long long o_tok_stride,
-                                    long long o_head_stride) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int i = blockIdx.x, head = blockIdx.y;
-    const size_t base = (static_cast<size_t>(i) * H + head) * max_splits;
-    const float sink = sinks ? sinks[head] * 1.4426950408889634f : -INFINITY;
-    float M = sink;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[2 * (base + s)]);
-    float L = sinks ? exp2f(sink - M) : 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float m = part_ml[2 * (base + s)];
-        if (m != -INFINITY) L += exp2f(m - M) * part_ml[2 * (base + s) + 1];
-    }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
-    for (int d = threadIdx.x; d < R; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float m = part_ml[2 * (base + s)];
-            if (m != -INFINITY) acc += exp2f(m - M) * part_o[(base + s) * R + d];
-        }
-        out[static_cast<size_t>(row_base + i) * o_tok_stride + static_cast<size_t>(head) * o_head_stride + d] =
-            __float2bfloat16_rn(acc * inv);
-    }
-}
-
-template <int RT, int CSPLIT>
-int launch_latent_mma(dim3 grid, cudaStream_t stream, const void* q, long long qts, long long qhs,
-                      const void* cache, const int* block_table, int bt_stride, const int* cu_q,
-                      const int* ctx_len, const int* tiles, int req_base, int row_base, int tokb,
-                      int H, int R, int page_size, float scale, int window, const float* sinks,
-                      void* out, long long ots, long long ohs, int chunk, float* part_o,
-                      float* part_ml, int max_splits) {
-    const size_t smem = static_cast<size_t>(kLtRows + 2 * kLtBN) * RT * 2;
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(latent_attention_mma_kernel<RT, CSPLIT>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_pdl(latent_attention_mma_kernel<RT, CSPLIT>, grid, dim3(128 * CSPLIT), smem, stream,
-                      static_cast<const __nv_bfloat16*>(q), qts, qhs,
-                      static_cast<const __nv_bfloat16*>(cache), block_table, bt_stride, cu_q, ctx_len,
-                      tiles, req_base, row_base, tokb, H, R, page_size,
-                      scale * 1.4426950408889634f, window, sinks, static_cast<__nv_bfloat16*>(out),
-                      ots, ohs, chunk, part_o, part_ml, max_splits);
-}
-
-}  // namespace somi
-
-SOMI_API int somi_latent_attention_mma_q_tile() { return 16; }
-SOMI_API int somi_latent_attention_mma_chunk() { return 256; }
-
-SOMI_API int somi_latent_attention_mma_supported(int heads, int R) {
-    return heads >= 1 && heads <= 65535 * 4 && R >= 8 && R <= 512 && R % 8 == 0;
-}
-
-// bfloat16.  `tiles`: int32 [n_tiles, 3] = (request, first row, rows <= 16) over the multi-token
-// requests; the n_decode single-token requests follow them (request n_prefill_req + i, row
-// n_prefill_tok + i).  `max_kv_len`: the longest request's keys after this step.  `scratch`:
-// float32, at least n_decode * heads * splits * (R + 2) elements where splits =
-// somi_latent_attention_mma_splits(...) > 1.
-SOMI_API int somi_latent_attention_mma_splits(int max_kv_len, int window) {
-    const int span = window > 0 ? min(window + kLtBN, max_kv_len) : max_kv_len;
-    return max(1, (span + 255) / 256);
-}
-
-SOMI_API int somi_latent_attention_mma(
-    const void* q, long long q_tok_stride, long long q_head_stride, const void* cache,
-    const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
-    int n_tiles, int n_prefill_req, int n_prefill_tok, int n_decode, int max_kv_len, int heads,
-    int R, int page_size, float scale, int window, const float* sinks, void* out,
-    long long o_tok_stride, long long o_head_stride, float* scratch, cudaStream_t stream) {
-    if (n_tiles + n_decode <= 0) return 0;
-    if (!somi_latent_attention_mma_supported(heads, R) || page_size <= 0 ||
-        (q_tok_stride | q_head_stride | o_tok_stride | o_head_stride) % 8 ||
-        (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) % 16)
-        return SOMI_ERR_UNSUPPORTED;
-    const int splits = n_decode > 0 ? somi_latent_attention_mma_splits(max_kv_len, window) : 1;
-    if (splits > 65535) return SOMI_ERR_UNSUPPORTED;
-    float* part_o = scratch;
-    float* part_ml = scratch ? scratch + static_cast<size_t>(n_decode) * heads * splits * R : nullptr;
-    if (splits > 1 && !scratch) return SOMI_ERR_UNSUPPORTED;
-    int rc = 0;
-#define SOMI_LATT_MMA(RT, CS)                                                                   \
-    do {                                                                                        \
-        if (n_tiles > 0)                                                                        \
-            rc = launch_latent_mma<RT, CS>(dim3(n_tiles, (heads + 3) / 4), stream, q,           \
-                q_tok_stride, q_head_stride, cache, block_table, bt_stride, cu_q, ctx_len,      \
-                tiles, 0, 0, 16, heads, R, page_size, scale, window, sinks, out, o_tok_stride,  \
-                o_head_stride, 0, nullptr, nullptr, 1);                                         \
-        if (rc == 0 && n_decode > 0)                                                            \
-            rc = launch_latent_mma<RT, CS>(dim3(n_decode, (heads + 63) / 64, splits), stream,   \
-                q, q_tok_stride, q_head_stride, cache, block_table, bt_stride, cu_q, ctx_len,   \
-                nullptr, n_prefill_req, n_prefill_tok, 1, heads, R, page_size, scale, window,   \
-                sinks, out, o_tok_stride, o_head_stride, splits > 1 ? 256 : 0, part_o, part_ml, \
-                splits);                                                                        \
-    } while (0)
-    if (R <= 64) SOMI_LATT_MMA(64, 1);
-    else if (R <= 128) SOMI_LATT_MMA(128, 1);
-    else if (R <= 256) SOMI_LATT_MMA(256, 1);
-    else SOMI_LATT_MMA(512, 2);
-#undef SOMI_LATT_MMA
-    if (rc != 0) return rc;
-    if (n_decode > 0 && splits > 1)
-        launch_pdl(latent_merge_kernel, dim3(n_decode, heads), dim3(min(256, ((R + 31) / 32) * 32)), 0,
-                   stream, part_o, part_ml, splits, splits, heads, R, sinks, n_prefill_tok,
-                   static_cast<__nv_bfloat16*>(out), o_tok_stride, o_head_stride);
     return launch_status();
 }

@@ -8,6 +8,7 @@
 // Everything a norm, a gate or a position computes is float32; inputs and outputs are float32 or
 // bfloat16.  One CTA per token (row) unless stated otherwise.
 #include "common.cuh"
+#include "vec4.cuh"
 
 namespace somi {
 
@@ -71,7 +72,7 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
                                      const TG* __restrict__ gate, long long gate_stride,
                                      const void* __restrict__ weight, int weight_dtype, float eps,
                                      TO* __restrict__ out, const int* __restrict__ rows, int H,
-                                     int write_back, int rms) {
+                                     int write_back, int rms, int vec4) {
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     pdl_launch_dependents();
@@ -81,6 +82,70 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
     float* r = residual + row * H;
     const TD* d = delta ? delta + row * H : nullptr;
     const TG* g = gate ? gate + row * gate_stride : nullptr;
+    TO* o = out + static_cast<size_t>(b) * H;
+    if (vec4 && H <= static_cast<int>(blockDim.x) * 16) {
+        // Up to four vectors of four columns a thread, every load of the row issued before the
+        // first sum is needed; the row stays in registers between the passes.
+        F4 v[4];
+        const int step = blockDim.x * 4;
+        const int i0 = threadIdx.x * 4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (i0 + k * step < H) v[k] = load4(r + i0 + k * step);
+        if (d) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + k * step;
+                if (i < H) {
+                    F4 sum = load4(d + i);
+                    for (int sp = 1; sp < splits; ++sp) {
+                        const F4 t = load4(d + sp * split_stride + i);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sum.v[e] += t.v[e];
+                    }
+                    if (g) {
+                        const F4 gg = load4(g + i);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sum.v[e] *= sigmoid_f(gg.v[e]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[k].v[e] += sum.v[e];
+                    if (write_back) store4(r + i, v[k]);
+                }
+            }
+        }
+        float mean = 0.f;
+        if (!rms) {
+            float sm = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (i0 + k * step < H) sm += (v[k].v[0] + v[k].v[1]) + (v[k].v[2] + v[k].v[3]);
+            mean = block_sum(sm, scratch) / static_cast<float>(H);
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (i0 + k * step < H) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float dv = v[k].v[e] - mean;
+                    ss = fmaf(dv, dv, ss);
+                }
+            }
+        const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(H) + eps);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * step;
+            if (i < H) {
+                const F4 w = load4_any(weight, weight_dtype, i);
+                F4 y;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) y.v[e] = (v[k].v[e] - mean) * rstd * w.v[e];
+                store4(o + i, y);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = r[i];
         if (d) {
@@ -101,13 +166,12 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
     } else {
         mean_rstd(row_buf, H, eps, scratch, mean, rstd);
     }
-    TO* o = out + static_cast<size_t>(b) * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x)
         o[i] = from_float<TO>((row_buf[i] - mean) * rstd * load_as_float(weight, weight_dtype, i));
 }
 
 // ------------------------------------------------- short causal convolution
-// out[t] = h[t] + sum_{d=0}^{taps-1} w[:, taps-1-d] * h_(t-d), where h_(t-d) is the row d places
+// out[t] = h[t] + sum_{d=0}^{taps-1} w[taps-1-d, :] * h_(t-d) (w: [taps, H]), where h_(t-d) is the row d places
 // back in the same request: a row of this step, or (before the step's first row) the request's
 // state, which holds its last taps-1 inputs, oldest first, zero before the sequence's start.
 // The state is only read here; `causal_taps_state_kernel` moves it on afterwards.
@@ -116,14 +180,32 @@ __global__ void causal_taps_kernel(const T* __restrict__ h, const float* __restr
                                    const T* __restrict__ state, const int* __restrict__ cu_q,
                                    const int* __restrict__ token_request,
                                    const int* __restrict__ state_slot, T* __restrict__ out, int H,
-                                   int taps) {
+                                   int taps, int vec4) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int req = token_request[t];
     const int local = t - cu_q[req];
     const T* st = state + static_cast<size_t>(state_slot[req]) * (taps - 1) * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    if (vec4) {
+        for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < H; c += gridDim.y * blockDim.x * 4) {
+            const F4 own = load4(h + static_cast<size_t>(t) * H + c);
+            F4 acc = F4{{0.f, 0.f, 0.f, 0.f}};
+            for (int d = taps - 1; d >= 0; --d) {      // oldest input first
+                const F4 v = d == 0 ? own
+                             : (local - d >= 0 ? load4(h + static_cast<size_t>(t - d) * H + c)
+                                               : load4(st + static_cast<size_t>(taps - 1 + local - d) * H + c));
+                const F4 ww = load4(w + static_cast<size_t>(taps - 1 - d) * H + c);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc.v[e] = fmaf(ww.v[e], v.v[e], acc.v[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc.v[e] += own.v[e];
+            store4(out + static_cast<size_t>(t) * H + c, acc);
+        }
+        return;
+    }
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H; c += gridDim.y * blockDim.x) {
         const float own = to_float(h[static_cast<size_t>(t) * H + c]);
         float acc = 0.f;
         for (int d = taps - 1; d >= 0; --d) {          // oldest input first
@@ -131,7 +213,7 @@ __global__ void causal_taps_kernel(const T* __restrict__ h, const float* __restr
             if (d == 0) v = own;
             else if (local - d >= 0) v = to_float(h[static_cast<size_t>(t - d) * H + c]);
             else v = to_float(st[static_cast<size_t>(taps - 1 + local - d) * H + c]);
-            acc = fmaf(w[static_cast<size_t>(c) * taps + (taps - 1 - d)], v, acc);
+            acc = fmaf(w[static_cast<size_t>(taps - 1 - d) * H + c], v, acc);
         }
         out[static_cast<size_t>(t) * H + c] = from_float<T>(own + acc);
     }
@@ -163,23 +245,42 @@ __global__ void causal_taps_state_kernel(const T* __restrict__ h, T* __restrict_
 
 // ------------------------------------------ RMS norm of latents + cache write
 // x[t] = [a (na columns) | b (nb columns)], rows `stride` elements apart.  a_out[t] = rmsnorm(a) * wa;
-// rmsnorm(b) * wb goes to cache + slot_map[t] * nb (and nowhere when nb == 0).  One warp per part.
+// rmsnorm(b) * wb goes to cache + slot_map[t] * nb (and nowhere when nb == 0).  One warp per part,
+// two tokens per CTA.
 template <typename T>
 __global__ void latent_norm_store_kernel(const T* __restrict__ x, long long stride, int na, int nb,
                                          const void* __restrict__ wa, const void* __restrict__ wb,
                                          int weight_dtype, float eps, T* __restrict__ a_out,
-                                         const int* __restrict__ slot_map, T* __restrict__ cache) {
+                                         const int* __restrict__ slot_map, T* __restrict__ cache,
+                                         int T_rows, int vec4) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp == 1 && nb == 0) return;
-    const T* src = x + static_cast<size_t>(t) * stride + (warp == 0 ? 0 : na);
-    const int n = warp == 0 ? na : nb;
-    const void* w = warp == 0 ? wa : wb;
-    T* dst = warp == 0 ? a_out + static_cast<size_t>(t) * na
+    const int t = blockIdx.x * (blockDim.x >> 6) + (warp >> 1);      // two warps per token
+    const int part = warp & 1;
+    if (t >= T_rows || (part == 1 && nb == 0)) return;
+    const T* src = x + static_cast<size_t>(t) * stride + (part == 0 ? 0 : na);
+    const int n = part == 0 ? na : nb;
+    const void* w = part == 0 ? wa : wb;
+    T* dst = part == 0 ? a_out + static_cast<size_t>(t) * na
                        : cache + static_cast<size_t>(slot_map[t]) * nb;
     float ss = 0.f;
+    if (vec4) {
+        for (int i = lane * 4; i < n; i += 128) {
+            const F4 v = load4(src + i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(v.v[e], v.v[e], ss);
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(n) + eps);
+        for (int i = lane * 4; i < n; i += 128) {
+            F4 v = load4(src + i);
+            const F4 ww = load4_any(w, weight_dtype, i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v.v[e] = v.v[e] * inv * ww.v[e];
+            store4(dst + i, v);
+        }
+        return;
+    }
     for (int i = lane; i < n; i += 32) {
         const float v = to_float(src[i]);
         ss = fmaf(v, v, ss);
@@ -193,14 +294,26 @@ __global__ void latent_norm_store_kernel(const T* __restrict__ x, long long stri
 // z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2; (p, q) = act[0..1].
 template <typename T>
 __global__ void xielu_kernel(const T* __restrict__ x, long long stride, const void* __restrict__ act,
-                             int act_dtype, T* __restrict__ out, int n) {
+                             int act_dtype, T* __restrict__ out, int n, int vec4) {
     pdl_launch_dependents();
     const float ap = softplus_f(load_as_float(act, act_dtype, 0));        // [constant]
     const float aq = 0.5f + softplus_f(load_as_float(act, act_dtype, 1));  // [constant]
     pdl_wait();
     const T* src = x + static_cast<size_t>(blockIdx.x) * stride;
     T* dst = out + static_cast<size_t>(blockIdx.x) * n;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    if (vec4) {
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < n; i += gridDim.y * blockDim.x * 4) {
+            F4 z = load4(src + i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = z.v[e];
+                z.v[e] = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(aq, expm1f(v) - v, 0.5f * v);
+            }
+            store4(dst + i, z);
+        }
+        return;
+    }
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
         const float z = to_float(src[i]);
         const float y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
         dst[i] = from_float<T>(y);
@@ -245,15 +358,23 @@ SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dt
     const size_t smem = static_cast<size_t>(H) * sizeof(float);
     if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
     if (!gate) gate_dtype = out_dtype;
+    const int vec4 = (H & 3) == 0 && (gate_stride & 3) == 0 && (delta_split_stride & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(gate) |
+                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+    // few rows (a decode step waits for this kernel): a thread per four columns, the row read
+    // in one pass; many rows: fewer threads per row, more rows per SM
+    int threads = row_threads(H);
+    if (vec4 && (n_out <= 32 || (delta_splits > 1 && n_out <= 256)))
+        threads = min(1024, ((H / 4 + 31) / 32) * 32);
 #define SOMI_LAUNCH_LN(TD, TG, TO)                                                               \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
             cudaFuncSetAttribute(add_layernorm_kernel<TD, TG, TO>,                               \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        launch_pdl(add_layernorm_kernel<TD, TG, TO>, dim3(n_out), dim3(row_threads(H)), smem,    \
+        launch_pdl(add_layernorm_kernel<TD, TG, TO>, dim3(n_out), dim3(threads), smem,           \
                    stream, residual, static_cast<const TD*>(delta), delta_splits,                \
                    delta_split_stride, static_cast<const TG*>(gate), gate_stride, weight,        \
-                   weight_dtype, eps, static_cast<TO*>(out), rows, H, write_back, rms);          \
+                   weight_dtype, eps, static_cast<TO*>(out), rows, H, write_back, rms, vec4);    \
     } while (0)
     // the gate and the output are of the compute dtype; the delta is that or float32 partial sums
     if (out_dtype == SOMI_F32) {
@@ -270,20 +391,25 @@ SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dt
 
 SOMI_API int somi_causal_taps_max() { return kMaxTaps; }
 
-// h, out: [T, H]; w: float32 [H, taps]; state: [slots, taps - 1, H] of h's dtype.
+// h, out: [T, H]; w: float32 [taps, H]; state: [slots, taps - 1, H] of h's dtype.
 SOMI_API int somi_causal_taps(const void* h, int dtype, const float* w, void* state, const int* cu_q,
                               const int* token_request, const int* state_slot, void* out, int T,
                               int R, int H, int taps, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (taps < 1 || taps > kMaxTaps || R <= 0) return SOMI_ERR_UNSUPPORTED;
-    const int threads = min(1024, ((H + 31) / 32) * 32);
-    const int tb = min(256, threads);
+    const int vec4 = (H & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(out) |
+                       reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+    const int per_thread = vec4 ? 4 : 1;
+    const int threads = min(256, ((H / per_thread + 31) / 32) * 32);
+    const int ychunks = max(1, min(16, (H / per_thread + threads - 1) / threads));
+    const int tb = min(256, ((H + 31) / 32) * 32);
     const int chunks = max(1, min(64, (H + tb - 1) / tb));
 #define SOMI_LAUNCH_TAPS(TT)                                                                     \
     do {                                                                                         \
-        launch_pdl(causal_taps_kernel<TT>, dim3(T), dim3(min(threads, 256)), 0, stream,          \
+        launch_pdl(causal_taps_kernel<TT>, dim3(T, ychunks), dim3(threads), 0, stream,           \
                    static_cast<const TT*>(h), w, static_cast<const TT*>(state), cu_q,            \
-                   token_request, state_slot, static_cast<TT*>(out), H, taps);                   \
+                   token_request, state_slot, static_cast<TT*>(out), H, taps, vec4);             \
         if (taps > 1)                                                                            \
             launch_pdl(causal_taps_state_kernel<TT>, dim3(R, chunks), dim3(tb), 0, stream,       \
                        static_cast<const TT*>(h), static_cast<TT*>(state), cu_q, state_slot, H,  \
@@ -301,10 +427,14 @@ SOMI_API int somi_latent_norm_store(const void* x, int dtype, long long stride, 
                                     cudaStream_t stream) {
     if (T <= 0) return 0;
     if (na <= 0 || nb < 0 || (nb > 0 && (!slot_map || !cache))) return SOMI_ERR_UNSUPPORTED;
+    const int vec4 = ((na | nb | static_cast<int>(stride & 3)) & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a_out) |
+                       reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(wa) |
+                       reinterpret_cast<uintptr_t>(wb)) & 15) == 0;
 #define SOMI_LAUNCH_LAT(TT)                                                                      \
-    launch_pdl(latent_norm_store_kernel<TT>, dim3(T), dim3(64), 0, stream,                       \
+    launch_pdl(latent_norm_store_kernel<TT>, dim3((T + 1) / 2), dim3(128), 0, stream,            \
                static_cast<const TT*>(x), stride, na, nb, wa, wb, weight_dtype, eps,             \
-               static_cast<TT*>(a_out), slot_map, static_cast<TT*>(cache))
+               static_cast<TT*>(a_out), slot_map, static_cast<TT*>(cache), T, vec4)
     if (dtype == SOMI_F32) SOMI_LAUNCH_LAT(float);
     else SOMI_LAUNCH_LAT(__nv_bfloat16);
 #undef SOMI_LAUNCH_LAT
@@ -314,13 +444,19 @@ SOMI_API int somi_latent_norm_store(const void* x, int dtype, long long stride, 
 SOMI_API int somi_xielu(const void* x, int dtype, long long stride, const void* act, int act_dtype,
                         void* out, int T, int n, cudaStream_t stream) {
     if (T <= 0 || n <= 0) return 0;
-    const int threads = min(1024, max(128, ((n / 8 + 31) / 32) * 32));
+    const int vec4 = ((n | static_cast<int>(stride & 3)) & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int threads = 256;
+    const int per_cta = threads * (vec4 ? 4 : 1);
+    // few rows: the row's columns over several CTAs; many rows: one CTA walks the row
+    const int ychunks = T >= 512 ? max(1, min(4, n / (4 * per_cta))) : max(1, min(64, (n + per_cta - 1) / per_cta));
     if (dtype == SOMI_F32)
-        launch_pdl(xielu_kernel<float>, dim3(T), dim3(threads), 0, stream,
-                   static_cast<const float*>(x), stride, act, act_dtype, static_cast<float*>(out), n);
+        launch_pdl(xielu_kernel<float>, dim3(T, ychunks), dim3(threads), 0, stream,
+                   static_cast<const float*>(x), stride, act, act_dtype, static_cast<float*>(out), n,
+                   vec4);
     else
-        launch_pdl(xielu_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+        launch_pdl(xielu_kernel<__nv_bfloat16>, dim3(T, ychunks), dim3(threads), 0, stream,
                    static_cast<const __nv_bfloat16*>(x), stride, act, act_dtype,
-                   static_cast<__nv_bfloat16*>(out), n);
+                   static_cast<__nv_bfloat16*>(out), n, vec4);
     return launch_status();
 }

@@ -483,11 +483,12 @@ class CudaOps:
                               f"{self.max_taps})")
 
     def causal_taps(self, h, weight, state, batch, out) -> None:
-        """out = h + conv(h) over each request's rows, continued from `state` [slots, taps-1, H]
-        (the request's last inputs), which is moved on by this step's rows."""
+        """out = h + conv(h) over each request's rows (`weight`: float32 [taps, H], the newest
+        input's tap last), continued from `state` [slots, taps-1, H] (the request's last inputs),
+        which is moved on by this step's rows."""
         _check(h, weight, state, out)
-        taps = weight.shape[1]
-        assert weight.dtype == torch.float32 and weight.shape[0] == h.shape[1]
+        taps = weight.shape[0]
+        assert weight.dtype == torch.float32 and weight.shape[1] == h.shape[1]
         if taps > 1:
             assert state is not None and state.dtype == h.dtype
             assert tuple(state.shape[1:]) == (taps - 1, h.shape[1])

@@ -50,7 +50,8 @@ class CausalTaps:
         self.channels = int(params["channels"])
         self.taps = int(params["taps"])
         ctx.ops.check_taps(self.taps)
-        self.weight = tensors[names_of(params)["weight"]].float().contiguous()
+        # [taps, channels] float32: a thread reads the taps of four neighbouring channels at once
+        self.weight = tensors[names_of(params)["weight"]].float().t().contiguous()
 
     def state_needs(self) -> StateNeeds:
         """The last taps - 1 inputs of a request, oldest first, in the compute dtype."""

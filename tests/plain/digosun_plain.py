@@ -63,18 +63,19 @@ def causal_taps(h: torch.Tensor, taps_weight: torch.Tensor) -> torch.Tensor:
 
 
 def windowed_sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-                            window: int | None, sink: torch.Tensor) -> torch.Tensor:
-    """q, k [S, H, d], v [S, H, dv] -> [S, H, dv].  Token i reads j with 0 <= i - j < window;
-    the softmax denominator of head h also holds exp(sink[h]), which carries no value."""
+                            window: int | None, sink: torch.Tensor, first: int = 0) -> torch.Tensor:
+    """q, k [S, H, d], v [S, H, dv] -> [S, H, dv] (rows before `first` are left zero).  Token i
+    reads j with 0 <= i - j < window; the softmax denominator of head h also holds exp(sink[h]),
+    which carries no value."""
     S, H, _ = q.shape
     out = torch.zeros((S, H, v.shape[2]), dtype=q.dtype)
-    for i in range(S):
+    for i in range(first, S):
         lo = 0 if window is None else max(0, i - window + 1)
-        for h in range(H):
-            s = (k[lo:i + 1, h] @ q[i, h]) * scale
-            m = torch.maximum(s.max(), sink[h])
-            e = torch.exp(s - m)
-            out[i, h] = (e[:, None] * v[lo:i + 1, h]).sum(0) / (e.sum() + torch.exp(sink[h] - m))
+        s = torch.einsum("jhd,hd->jh", k[lo:i + 1], q[i]) * scale          # [keys, H]
+        m = torch.maximum(s.max(dim=0).values, sink)
+        e = torch.exp(s - m)
+        denom = e.sum(dim=0) + torch.exp(sink - m)
+        out[i] = torch.einsum("jh,jhd->hd", e, v[lo:i + 1]) / denom[:, None]
     return out
 
 
