@@ -24,23 +24,28 @@ namespace somi {
 constexpr int kLtRows = 64;
 constexpr int kLtBN = 64;
 
-template <int RT>
+// One tile of 64 cached positions.  A row (position) belongs to THREADS / 64 threads, which
+// take its 16-byte pieces in turn: one look-up in the block table and one division a thread.
+template <int RT, int THREADS>
 __device__ __forceinline__ void load_latent_tile(unsigned char* dst,
                                                  const __nv_bfloat16* __restrict__ cache,
                                                  const int* __restrict__ bt, int kb, int k_lo,
-                                                 int k_hi, int R, int page_size, int tid,
-                                                 int threads) {
+                                                 int k_hi, int R, int page_size, int tid) {
     constexpr int CPR = RT / 8;
-    for (int c = tid; c < kLtBN * CPR; c += threads) {
-        const int r = c / CPR, ch = c - r * CPR;
-        const int j = kb + r;
-        const bool ok = j >= k_lo && j < k_hi && ch * 8 < R;
-        size_t off = 0;
-        if (ok) {
-            const int page = bt[j / page_size];
-            off = (static_cast<size_t>(page) * page_size + j % page_size) * R + ch * 8;
-        }
-        cp_async_16(smem_u32(dst + swizzled_offset<RT>(r, ch)), cache + off, ok ? 16 : 0);
+    constexpr int TPR = THREADS / kLtBN;                 // threads per row
+    const int r = tid / TPR, sub = tid - r * TPR;
+    const int j = kb + r;
+    const bool row_ok = j >= k_lo && j < k_hi;
+    size_t base = 0;
+    if (row_ok) {
+        const int page = bt[j / page_size];
+        base = (static_cast<size_t>(page) * page_size + j % page_size) * R;
+    }
+#pragma unroll 4
+    for (int ch = sub; ch < CPR; ch += TPR) {
+        const bool ok = row_ok && ch * 8 < R;
+        cp_async_16(smem_u32(dst + swizzled_offset<RT>(r, ch)), cache + (ok ? base + ch * 8 : 0),
+                    ok ? 16 : 0);
     }
 }
 
@@ -104,7 +109,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
                       static_cast<size_t>(head) * q_head_stride + ch * 8;
         cp_async_16(smem_u32(Qs + swizzled_offset<RT>(r, ch)), src, ok ? 16 : 0);
     }
-    if (n_tiles > 0) load_latent_tile<RT>(Cs, cache, bt, kb0, k_lo, k_hi, R, page_size, tid, THREADS);
+    if (n_tiles > 0) load_latent_tile<RT, THREADS>(Cs, cache, bt, kb0, k_lo, k_hi, R, page_size, tid);
     cp_async_commit();
 
     float o[OC][4];
@@ -129,8 +134,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
         const int kb = kb0 + t * kLtBN;
         const int buf = t & 1;
         if (t + 1 < n_tiles)
-            load_latent_tile<RT>(Cs + (buf ^ 1) * TILE, cache, bt, kb + kLtBN, k_lo, k_hi, R,
-                                 page_size, tid, THREADS);
+            load_latent_tile<RT, THREADS>(Cs + (buf ^ 1) * TILE, cache, bt, kb + kLtBN, k_lo, k_hi, R,
+                                          page_size, tid);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -306,8 +311,6 @@ int launch_latent_mma(dim3 grid, cudaStream_t stream, const void* q, long long q
 using namespace somi;
 
 SOMI_API int somi_latent_attention_mma_q_tile() { return 16; }
-SOMI_API int somi_latent_attention_mma_chunk() { return 256; }
-
 SOMI_API int somi_latent_attention_mma_supported(int heads, int R) {
     return heads >= 1 && heads <= 65535 * 4 && R >= 8 && R <= 512 && R % 8 == 0;
 }
@@ -316,10 +319,22 @@ SOMI_API int somi_latent_attention_mma_supported(int heads, int R) {
 // requests; the n_decode single-token requests follow them (request n_prefill_req + i, row
 // n_prefill_tok + i).  `max_kv_len`: the longest request's keys after this step.  `scratch`:
 // float32, at least n_decode * heads * splits * (R + 2) elements where splits =
-// somi_latent_attention_mma_splits(...) > 1.
-SOMI_API int somi_latent_attention_mma_splits(int max_kv_len, int window) {
+// somi_latent_attention_mma_splits(max_kv_len, window, n_decode, heads) > 1.
+// Keys per chunk of a single-token request: a multiple of the key tile, as small as keeps the
+// step's CTAs (requests x head groups x chunks) within two per SM.  A short chunk means a short
+// chain of tiles per CTA, which is what a decode step waits for.
+static int latent_chunk(int max_kv_len, int window, int n_decode, int heads) {
     const int span = window > 0 ? min(window + kLtBN, max_kv_len) : max_kv_len;
-    return max(1, (span + 255) / 256);
+    const int tiles = max(1, (span + kLtBN - 1) / kLtBN);
+    const int groups = max(1, n_decode) * ((heads + kLtRows - 1) / kLtRows);
+    const int splits = max(1, min(tiles, (2 * 148) / groups));
+    return ((tiles + splits - 1) / splits) * kLtBN;
+}
+
+SOMI_API int somi_latent_attention_mma_splits(int max_kv_len, int window, int n_decode, int heads) {
+    const int span = window > 0 ? min(window + kLtBN, max_kv_len) : max_kv_len;
+    const int chunk = latent_chunk(max_kv_len, window, n_decode, heads);
+    return max(1, (span + chunk - 1) / chunk);
 }
 
 SOMI_API int somi_latent_attention_mma(
@@ -333,7 +348,8 @@ SOMI_API int somi_latent_attention_mma(
         (q_tok_stride | q_head_stride | o_tok_stride | o_head_stride) % 8 ||
         (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) % 16)
         return SOMI_ERR_UNSUPPORTED;
-    const int splits = n_decode > 0 ? somi_latent_attention_mma_splits(max_kv_len, window) : 1;
+    const int splits = n_decode > 0 ? somi_latent_attention_mma_splits(max_kv_len, window, n_decode, heads) : 1;
+    const int chunk = latent_chunk(max_kv_len, window, n_decode, heads);
     if (splits > 65535) return SOMI_ERR_UNSUPPORTED;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + static_cast<size_t>(n_decode) * heads * splits * R : nullptr;
@@ -350,7 +366,7 @@ SOMI_API int somi_latent_attention_mma(
             rc = launch_latent_mma<RT, CS>(dim3(n_decode, (heads + 63) / 64, splits), stream,   \
                 q, q_tok_stride, q_head_stride, cache, block_table, bt_stride, cu_q, ctx_len,   \
                 nullptr, n_prefill_req, n_prefill_tok, 1, heads, R, page_size, scale, window,   \
-                sinks, out, o_tok_stride, o_head_stride, splits > 1 ? 256 : 0, part_o, part_ml, \
+                sinks, out, o_tok_stride, o_head_stride, splits > 1 ? chunk : 0, part_o, part_ml,\
                 splits);                                                                        \
     } while (0)
     if (R <= 64) SOMI_LATT_MMA(64, 1);

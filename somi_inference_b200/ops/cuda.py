@@ -590,8 +590,8 @@ class CudaOps:
             # tensor cores: 16 tokens x 4 heads per CTA for prompt portions; all heads of a
             # single-token request per CTA, its keys in chunks whose partial sums are merged
             max_kv = group.width * page_size      # a bound that changes with the layout only
-            splits = int(self.lib.somi_latent_attention_mma_splits(ctypes.c_int(max_kv),
-                                                                   ctypes.c_int(win)))
+            splits = int(self.lib.somi_latent_attention_mma_splits(
+                ctypes.c_int(max_kv), ctypes.c_int(win), ctypes.c_int(n_decode), ctypes.c_int(heads)))
             ws = self._scratch(n_decode * heads * splits * (rank + 2), q.device) if splits > 1 and n_decode else None
             rc = self.lib.somi_latent_attention_mma(
                 _ptr(q), ctypes.c_longlong(rank), ctypes.c_longlong(T * rank), _ptr(cache),
