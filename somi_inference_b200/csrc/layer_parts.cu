@@ -219,6 +219,36 @@ __global__ void causal_taps_kernel(const T* __restrict__ h, const float* __restr
     }
 }
 
+// A step in which every request brings one token: output and new state in one kernel.  A thread
+// owns four channels of one request: it reads the state's rows, then shifts them by one.
+template <typename T>
+__global__ void causal_taps_single_kernel(const T* __restrict__ h, const float* __restrict__ w,
+                                          T* __restrict__ state, const int* __restrict__ state_slot,
+                                          T* __restrict__ out, int H, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    T* st = state + static_cast<size_t>(state_slot[t]) * (taps - 1) * H;
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < H; c += gridDim.y * blockDim.x * 4) {
+        const F4 own = load4(h + static_cast<size_t>(t) * H + c);
+        const F4 w_own = load4(w + static_cast<size_t>(taps - 1) * H + c);
+        F4 acc;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc.v[e] = w_own.v[e] * own.v[e];
+        for (int s = 0; s < taps - 1; ++s) {               // state row s is the input taps-1-s back
+            const F4 v = load4(st + static_cast<size_t>(s) * H + c);
+            const F4 ww = load4(w + static_cast<size_t>(s) * H + c);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc.v[e] = fmaf(ww.v[e], v.v[e], acc.v[e]);
+            if (s > 0) store4(st + static_cast<size_t>(s - 1) * H + c, v);
+        }
+        if (taps > 1) store4(st + static_cast<size_t>(taps - 2) * H + c, own);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc.v[e] += own.v[e];
+        store4(out + static_cast<size_t>(t) * H + c, acc);
+    }
+}
+
 // New state of request r: its last taps-1 inputs after this step's rows, oldest first.  A thread
 // owns one channel of one request and reads what it needs of the old state before it writes.
 constexpr int kMaxTaps = 32;
@@ -302,14 +332,23 @@ __global__ void xielu_kernel(const T* __restrict__ x, long long stride, const vo
     const T* src = x + static_cast<size_t>(blockIdx.x) * stride;
     T* dst = out + static_cast<size_t>(blockIdx.x) * n;
     if (vec4) {
-        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < n; i += gridDim.y * blockDim.x * 4) {
-            F4 z = load4(src + i);
+        // eight columns a thread and step: two vectors in flight
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8; i < n; i += gridDim.y * blockDim.x * 8) {
+            F4 z[2];
+            z[0] = load4(src + i);
+            if (i + 4 < n) z[1] = load4(src + i + 4);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float v = z.v[e];
-                z.v[e] = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(aq, expm1f(v) - v, 0.5f * v);
+            for (int k = 0; k < 2; ++k) {
+                if (i + 4 * k >= n) break;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float v = z[k].v[e];
+                    // bfloat16 results carry 8 bits: the fast exponential is enough there
+                    const float em1 = sizeof(T) == 2 ? __expf(v) - 1.0f : expm1f(v);
+                    z[k].v[e] = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(aq, em1 - v, 0.5f * v);
+                }
+                store4(dst + i + 4 * k, z[k]);
             }
-            store4(dst + i, z);
         }
         return;
     }
@@ -407,6 +446,12 @@ SOMI_API int somi_causal_taps(const void* h, int dtype, const float* w, void* st
     const int chunks = max(1, min(64, (H + tb - 1) / tb));
 #define SOMI_LAUNCH_TAPS(TT)                                                                     \
     do {                                                                                         \
+        if (T == R && vec4) {                                                                    \
+            launch_pdl(causal_taps_single_kernel<TT>, dim3(T, ychunks), dim3(threads), 0, stream,\
+                       static_cast<const TT*>(h), w, static_cast<TT*>(state), state_slot,        \
+                       static_cast<TT*>(out), H, taps);                                          \
+            break;                                                                               \
+        }                                                                                        \
         launch_pdl(causal_taps_kernel<TT>, dim3(T, ychunks), dim3(threads), 0, stream,           \
                    static_cast<const TT*>(h), w, static_cast<const TT*>(state), cu_q,            \
                    token_request, state_slot, static_cast<TT*>(out), H, taps, vec4);             \
@@ -447,9 +492,9 @@ SOMI_API int somi_xielu(const void* x, int dtype, long long stride, const void* 
     const int vec4 = ((n | static_cast<int>(stride & 3)) & 3) == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     const int threads = 256;
-    const int per_cta = threads * (vec4 ? 4 : 1);
-    // few rows: the row's columns over several CTAs; many rows: one CTA walks the row
-    const int ychunks = T >= 512 ? max(1, min(4, n / (4 * per_cta))) : max(1, min(64, (n + per_cta - 1) / per_cta));
+    const int per_cta = threads * (vec4 ? 8 : 1);
+    // few rows: the row's columns over several CTAs; many rows: a CTA walks a part of the row
+    const int ychunks = T >= 512 ? max(1, min(8, n / (2 * per_cta))) : max(1, min(64, (n + per_cta - 1) / per_cta));
     if (dtype == SOMI_F32)
         launch_pdl(xielu_kernel<float>, dim3(T, ychunks), dim3(threads), 0, stream,
                    static_cast<const float*>(x), stride, act, act_dtype, static_cast<float*>(out), n,

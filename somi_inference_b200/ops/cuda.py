@@ -498,8 +498,8 @@ class CudaOps:
             ctypes.c_int(batch.num_requests), ctypes.c_int(h.shape[1]), ctypes.c_int(taps),
             self._stream())
         self._done(rc, "causal_taps")
-        if taps > 1:
-            self.launches += 1
+        if taps > 1 and not (h.shape[0] == batch.num_requests and h.shape[1] % 4 == 0):
+            self.launches += 1      # the state's own kernel (a step of single tokens needs none)
         if trace.active():
             trace.note("causal_taps", 2 * h.numel() * h.element_size()
                        + 2 * batch.num_requests * (taps - 1) * h.shape[1] * h.element_size())
