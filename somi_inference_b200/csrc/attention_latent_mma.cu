@@ -14,8 +14,10 @@
 //     result itself.
 // RT is the latent width rounded up to 64/128/256/512 (columns beyond the width are zeros in
 // shared memory).  Up to RT = 256 a warp owns 16 rows and all columns of O (four warps); at
-// RT = 512 the output columns are split over two warps that both compute their rows' scores
-// (eight warps: registers hold 16 x 256 accumulators at most).  Softmax: online, float32,
+// RT = 512 two warps share a row tile (eight warps: registers hold 16 x 256 accumulators at
+// most): each computes the scores of half of a tile's keys, they exchange row maxima, row sums
+// and P (in the MMA's register layout) through shared memory at two barriers of their own, and
+// each accumulates half of the output columns.  Softmax: online, float32,
 // base 2; the sink enters as the starting maximum with denominator 1 (or in the merge).
 #include "mma.cuh"
 
@@ -49,6 +51,12 @@ __device__ __forceinline__ void load_latent_tile(unsigned char* dst,
     }
 }
 
+// The two warps of a row tile (warps mt and mt + 4) meet at a barrier of their own.
+__device__ __forceinline__ void pair_barrier(int mt) {
+    asm volatile("bar.sync %0, 64;\n" ::"r"(mt + 1) : "memory");
+}
+constexpr int kLtExchangeBytes = 4096 + 4 * 2 * 2 * 4 * 32 * 4;     // maxima, sums, P (12 KB)
+
 template <int RT, int CSPLIT>
 __global__ void __launch_bounds__(128 * CSPLIT)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok_stride,
@@ -68,6 +76,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
     extern __shared__ __align__(128) unsigned char smem_raw[];
     unsigned char* Qs = smem_raw;                        // [64][RT]
     unsigned char* Cs = Qs + kLtRows * RT * 2;           // 2 x [64][RT]
+    unsigned char* xch = Cs + 2 * TILE;                  // CSPLIT == 2: what warp pairs exchange
     pdl_launch_dependents();
     pdl_wait();
 
@@ -141,9 +150,13 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
         __syncthreads();
         const unsigned char* Ct = Cs + buf * TILE;
         if (warp_live) {
-            float s[8][4];
+            // the 16-key groups whose scores this warp computes: all four, or (two warps a row
+            // tile) its half of them; the other half comes from the partner through `xch`
+            constexpr int NP = 4 / CSPLIT;
+            const int np0 = cs * NP;
+            float s[2 * NP][4];
 #pragma unroll
-            for (int a = 0; a < 8; ++a)
+            for (int a = 0; a < 2 * NP; ++a)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
 #pragma unroll 4
@@ -152,9 +165,9 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
                 ldmatrix_x4(a, smem_u32(Qs + swizzled_offset<RT>(qr + (lane & 7) + ((lane >> 3) & 1) * 8,
                                                                 2 * ks + (lane >> 4))));
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {
+                for (int np = 0; np < NP; ++np) {
                     uint32_t b[4];
-                    ldmatrix_x4(b, smem_u32(Ct + swizzled_offset<RT>(np * 16 + (lane & 7) + (lane >> 4) * 8,
+                    ldmatrix_x4(b, smem_u32(Ct + swizzled_offset<RT>((np0 + np) * 16 + (lane & 7) + (lane >> 4) * 8,
                                                                     2 * ks + ((lane >> 3) & 1))));
                     mma_bf16_16816(s[2 * np], a, b[0], b[1]);
                     mma_bf16_16816(s[2 * np + 1], a, b[2], b[3]);
@@ -162,10 +175,10 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
             }
             float t_lo = -INFINITY, t_hi = -INFINITY;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < 2 * NP; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int key = kb + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int key = kb + (2 * np0 + nt) * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = e < 2 ? pos_lo : pos_hi;
                     const bool ok = key <= pos && key >= k_lo && key < k_hi &&
                                     (window <= 0 || key > pos - window);
@@ -177,28 +190,68 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
             t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
             t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1));
             t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
+            if constexpr (CSPLIT == 2) {
+                // the row maxima of the partner's keys
+                float2* xmax = reinterpret_cast<float2*>(xch) + (mt * 2) * 32;
+                xmax[cs * 32 + lane] = make_float2(t_lo, t_hi);
+                pair_barrier(mt);
+                const float2 other = xmax[(cs ^ 1) * 32 + lane];
+                t_lo = fmaxf(t_lo, other.x);
+                t_hi = fmaxf(t_hi, other.y);
+            }
             const float n_lo = fmaxf(m_lo, t_lo), n_hi = fmaxf(m_hi, t_hi);
             const float b_lo = n_lo == -INFINITY ? 0.f : n_lo, b_hi = n_hi == -INFINITY ? 0.f : n_hi;
             const float a_lo = exp2f(m_lo - b_lo), a_hi = exp2f(m_hi - b_hi);
             m_lo = n_lo;
             m_hi = n_hi;
             float r_lo = 0.f, r_hi = 0.f;
-            uint32_t pa[4][4];
+            uint32_t own[NP][4];
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < 2 * NP; ++nt) {
                 const uint32_t lo = pack_bf16(exp2f(s[nt][0] - b_lo), exp2f(s[nt][1] - b_lo));
                 const uint32_t hi = pack_bf16(exp2f(s[nt][2] - b_hi), exp2f(s[nt][3] - b_hi));
                 const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&lo);
                 const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&hi);
                 r_lo += __low2float(lo2) + __high2float(lo2);
                 r_hi += __low2float(hi2) + __high2float(hi2);
-                pa[nt >> 1][(nt & 1) * 2] = lo;
-                pa[nt >> 1][(nt & 1) * 2 + 1] = hi;
+                own[nt >> 1][(nt & 1) * 2] = lo;
+                own[nt >> 1][(nt & 1) * 2 + 1] = hi;
             }
             r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 1);
             r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 2);
             r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 1);
             r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 2);
+            uint32_t pa[4][4];
+            if constexpr (CSPLIT == 1) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) pa[k][e] = own[k % NP][e];
+            }
+            if constexpr (CSPLIT == 2) {
+                // P of this warp's keys, in the MMA's own register layout (both warps of a row
+                // tile hold the same rows in the same lanes), and its row sums
+                float2* xsum = reinterpret_cast<float2*>(xch + 2048) + (mt * 2) * 32;
+                uint32_t* xp = reinterpret_cast<uint32_t*>(xch + 4096) + (mt * 2) * (NP * 4 * 32);
+                xsum[cs * 32 + lane] = make_float2(r_lo, r_hi);
+#pragma unroll
+                for (int k = 0; k < NP; ++k)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) xp[cs * (NP * 4 * 32) + (k * 4 + e) * 32 + lane] = own[k][e];
+                pair_barrier(mt);
+                const float2 other = xsum[(cs ^ 1) * 32 + lane];
+                // the same order of addition in both warps: first half's keys, then second half's
+                r_lo = cs == 0 ? r_lo + other.x : other.x + r_lo;
+                r_hi = cs == 0 ? r_hi + other.y : other.y + r_hi;
+#pragma unroll
+                for (int k = 0; k < NP; ++k)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t oth = xp[(cs ^ 1) * (NP * 4 * 32) + (k * 4 + e) * 32 + lane];
+                        pa[k % 4][e] = cs == 0 ? own[k][e] : oth;                  // keys 0..31
+                        pa[(NP + k) % 4][e] = cs == 0 ? oth : own[k][e];           // keys 32..63
+                    }
+            }
             l_lo = l_lo * a_lo + r_lo;
             l_hi = l_hi * a_hi + r_hi;
 #pragma unroll
@@ -294,7 +347,8 @@ int launch_latent_mma(dim3 grid, cudaStream_t stream, const void* q, long long q
                       int H, int R, int page_size, float scale, int window, const float* sinks,
                       void* out, long long ots, long long ohs, int chunk, float* part_o,
                       float* part_ml, int max_splits) {
-    const size_t smem = static_cast<size_t>(kLtRows + 2 * kLtBN) * RT * 2;
+    const size_t smem = static_cast<size_t>(kLtRows + 2 * kLtBN) * RT * 2 +
+                        (CSPLIT == 2 ? kLtExchangeBytes : 0);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(latent_attention_mma_kernel<RT, CSPLIT>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
