@@ -172,8 +172,6 @@ class DigosunConfig:
     def validate(self) -> None:
         if not self.norm_eps > 0.0:
             raise ConfigError("norm.eps must be positive")
-        if self.width % 2:
-            raise ConfigError("width must be even (sine and cosine entries alternate)")
         if self.max_positions <= 0:
             raise ConfigError("max_positions must be positive")
         for i, layer in enumerate(self.layers):

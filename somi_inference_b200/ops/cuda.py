@@ -429,7 +429,7 @@ class CudaOps:
         _check(ids, positions, table, inv_freq, weight, out)
         assert ids.dtype == torch.int32 and positions.dtype == torch.int32
         assert out.dtype == torch.float32 and inv_freq.dtype == torch.float32
-        assert inv_freq.numel() * 2 == table.shape[1]
+        assert inv_freq.numel() == (table.shape[1] + 1) // 2
         rc = self.lib.somi_embed_sinusoid_layernorm(
             _ptr(ids), _ptr(positions), _ptr(table), _code(table), _ptr(inv_freq), _ptr(weight),
             _code(weight), ctypes.c_float(eps), _ptr(out), ctypes.c_int(ids.shape[0]),

@@ -38,7 +38,7 @@ class TokenEmbedding:
 @EMBEDDINGS.register("sinusoid_embedding")
 class SinusoidEmbedding:
     """x = norm(E[token] + s(position)): s has sin(p * base^(-2i/H)) at entry 2i and the cosine
-    of the same angle at entry 2i + 1; `norm` is a norm part (its weight is this part's).  The
+    of the same angle at entry 2i + 1 (an odd width ends on a sine); `norm` is a norm part (its weight is this part's).  The
     frequencies are made once on the host (float64, rounded to float32); angles, sine, cosine
     and the norm are float32 in the kernel, which writes the residual stream."""
 
@@ -52,8 +52,6 @@ class SinusoidEmbedding:
         self.ctx = ctx
         self.weight = tensors[names_of(params)["weight"]]
         self.hidden = int(params["hidden_size"])
-        if self.hidden % 2:
-            raise ValueError("a sinusoid embedding needs an even width")
         norm = params["norm"]
         if norm.kind != "layernorm":
             raise ValueError(f"the sinusoid embedding's kernel applies a layer norm, not {norm.kind!r}")

@@ -7,6 +7,9 @@ Q: one tap (no convolution state), one head, a window of one (a token sees only 
    a window longer than any test sequence.
 R: five taps, a window that spans several pages, the reader's window longer than the owner's
    (the cache must be kept for the longer one), head sizes of 32 and 16.
+S: an odd width and latent widths that are no multiple of 4 or 8 (none of the kernels' vector
+   paths, the attention kernel on the CUDA cores in bfloat16 too), seven heads, two taps, pages
+   of four positions.
 """
 
 from __future__ import annotations
@@ -44,8 +47,12 @@ TINY_R = dict(architecture="Digosun", vocab=257, width=96, norm={"eps": 1e-6}, c
               layers=[_layer(_mixer(4, 32, 16, 48, 64, 0.2, window=33), 160),
                       _layer(_mixer(2, 16, 32, 32, 64, 0.3, window=70, kv_from=0), 96),
                       _layer(_mixer(6, 16, 16, 24, 80, 0.25, window=16), None)])
-TINY = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R}
-PAGE_SIZES = {"P": 8, "Q": 16, "R": 16}
+TINY_S = dict(architecture="Digosun", vocab=90, width=45, norm={"eps": 1e-4}, canon={"taps": 2},
+              layers=[_layer(_mixer(7, 6, 10, 9, 20, 0.45, window=12), 33),
+                      _layer(_mixer(1, 5, 3, 7, 20, 0.7, window=12, kv_from=0), 21),
+                      _layer(_mixer(2, 10, 2, 11, 12, 0.4), 50)])
+TINY = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "S": TINY_S}
+PAGE_SIZES = {"P": 8, "Q": 16, "R": 16, "S": 4}
 
 
 def random_weights(raw: dict, seed: int, dtype=torch.float32) -> dict[str, torch.Tensor]:

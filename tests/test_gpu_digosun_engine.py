@@ -19,7 +19,7 @@ from tests.plain import digosun_plain as plain
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"P": [5, 97, 40, 70, 1, 33, 100, 64, 81, 2], "Q": [3, 50, 17, 64, 1, 30],
-           "R": [150, 5, 129, 71, 200, 16, 90]}
+           "R": [150, 5, 129, 71, 200, 16, 90], "S": [30, 1, 77, 12, 13, 45]}
 # float32: logits are of size 5-20 here; bfloat16: every activation between two kernels is
 # rounded to 8 bits.  A wrong key, a window that is off by one or a lost state moves a logit by
 # its own size.

@@ -57,7 +57,7 @@ def make_batch(ops, requests, *, rank=None, window=None, page_size=8, state=None
 
 
 # ------------------------------------------------------------------ embedding and norms
-@pytest.mark.parametrize("width", [48, 256, 1030])
+@pytest.mark.parametrize("width", [48, 256, 1030, 37])
 def test_embedding_sinusoid_layernorm(ops, width):
     g = torch.Generator().manual_seed(width)
     table = torch.randn(50, width, generator=g)
