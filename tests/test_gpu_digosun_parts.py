@@ -258,10 +258,10 @@ def run_latent_attention(ops, requests, *, heads, rank, window, page_size, dtype
 
 @pytest.mark.parametrize("dtype, mma", [(torch.float32, False), (torch.bfloat16, False),
                                         (torch.bfloat16, True)])
-@pytest.mark.parametrize("rank, heads, page_size", [(40, 3, 8), (64, 6, 16), (24, 1, 4), (136, 2, 16),
+@pytest.mark.parametrize("rank, heads, page_size", [(40, 3, 8), (64, 7, 16), (24, 1, 4), (136, 2, 16),
                                                     (36, 5, 16)])
 def test_latent_attention_random(ops, dtype, mma, rank, heads, page_size):
-    sinks = torch.tensor([0.5, -2.0, 3.0, 0.0, 1.0, -1.0])[:heads]
+    sinks = torch.tensor([0.5, -2.0, 3.0, 0.0, 1.0, -1.0, 2.0])[:heads]
     for window in (None, 1, 7, 33):
         reqs = [(0, 50), (37, 1), (3, 20), (0, 1), (64, 17), (31, 2), (90, 1)]
         err = run_latent_attention(ops, reqs, heads=heads, rank=rank, window=window,
