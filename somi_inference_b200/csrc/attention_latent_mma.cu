@@ -159,7 +159,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_tok
             for (int a = 0; a < 2 * NP; ++a)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
-#pragma unroll 4
+#pragma unroll 8
             for (int ks = 0; ks < RT / 16; ++ks) {
                 uint32_t a[4];
                 ldmatrix_x4(a, smem_u32(Qs + swizzled_offset<RT>(qr + (lane & 7) + ((lane >> 3) & 1) * 8,

@@ -50,9 +50,12 @@ __global__ void embed_sinusoid_layernorm_kernel(const int* __restrict__ ids,
     const int t = blockIdx.x;
     const T* row = table + static_cast<size_t>(ids[t]) * H;
     const float p = static_cast<float>(positions[t]);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float angle = p * inv_freq[i >> 1];      // float32, rounded once
-        row_buf[i] = to_float(row[i]) + ((i & 1) ? cosf(angle) : sinf(angle));
+    for (int pair = threadIdx.x; 2 * pair < H; pair += blockDim.x) {
+        const float angle = p * inv_freq[pair];        // float32, rounded once
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        row_buf[2 * pair] = to_float(row[2 * pair]) + sn;
+        if (2 * pair + 1 < H) row_buf[2 * pair + 1] = to_float(row[2 * pair + 1]) + cs;
     }
     __syncthreads();
     float mean, rstd;
@@ -180,10 +183,13 @@ __global__ void causal_taps_kernel(const T* __restrict__ h, const float* __restr
                                    const T* __restrict__ state, const int* __restrict__ cu_q,
                                    const int* __restrict__ token_request,
                                    const int* __restrict__ state_slot, T* __restrict__ out, int H,
-                                   int taps, int vec4) {
+                                   int taps, int vec4, int n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
+    // blockDim.y tokens a CTA: the look-ups that lead to a token's rows (request, first row,
+    // slot) are a chain of dependent loads, and several chains run side by side
+    const int t = blockIdx.x * blockDim.y + threadIdx.y;
+    if (t >= n_tokens) return;
     const int req = token_request[t];
     const int local = t - cu_q[req];
     const T* st = state + static_cast<size_t>(state_slot[req]) * (taps - 1) * H;
@@ -452,9 +458,10 @@ SOMI_API int somi_causal_taps(const void* h, int dtype, const float* w, void* st
                        static_cast<TT*>(out), H, taps);                                          \
             break;                                                                               \
         }                                                                                        \
-        launch_pdl(causal_taps_kernel<TT>, dim3(T, ychunks), dim3(threads), 0, stream,           \
+        launch_pdl(causal_taps_kernel<TT>, dim3((T + 3) / 4, max(1, min(4, H / 1024))),          \
+                   dim3(64, 4), 0, stream,                                                       \
                    static_cast<const TT*>(h), w, static_cast<const TT*>(state), cu_q,            \
-                   token_request, state_slot, static_cast<TT*>(out), H, taps, vec4);             \
+                   token_request, state_slot, static_cast<TT*>(out), H, taps, vec4, T);          \
         if (taps > 1)                                                                            \
             launch_pdl(causal_taps_state_kernel<TT>, dim3(R, chunks), dim3(tb), 0, stream,       \
                        static_cast<const TT*>(h), static_cast<TT*>(state), cu_q, state_slot, H,  \
