@@ -68,11 +68,13 @@ __global__ void embed_sinusoid_layernorm_kernel(const int* __restrict__ ids,
 // ------------------------------------------------ gated residual + layer norm
 // r = residual[row] + g * sum_s delta[s][row], g = sigmoid(gate[row]) (1 without a gate);
 // if write_back: residual[row] = r;  out[b] = (r - mean) * rstd * weight  (rms = 1: r * rrms * weight),
-// row = rows ? rows[b] : b.  delta: [splits] partial sums `split_stride` elements apart, added in order.
+// row = rows ? rows[b] : b.  delta: [splits] partial sums `split_stride` elements apart, added in order;
+// the gate's logits may be partial sums of the same kind.
 template <typename TD, typename TG, typename TO>
 __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                      int splits, long long split_stride,
                                      const TG* __restrict__ gate, long long gate_stride,
+                                     int gate_splits, long long gate_split_stride,
                                      const void* __restrict__ weight, int weight_dtype, float eps,
                                      TO* __restrict__ out, const int* __restrict__ rows, int H,
                                      int write_back, int rms, int vec4) {
@@ -107,7 +109,12 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
                         for (int e = 0; e < 4; ++e) sum.v[e] += t.v[e];
                     }
                     if (g) {
-                        const F4 gg = load4(g + i);
+                        F4 gg = load4(g + i);
+                        for (int sp = 1; sp < gate_splits; ++sp) {
+                            const F4 t = load4(g + sp * gate_split_stride + i);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) gg.v[e] += t.v[e];
+                        }
 #pragma unroll
                         for (int e = 0; e < 4; ++e) sum.v[e] *= sigmoid_f(gg.v[e]);
                     }
@@ -154,7 +161,11 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const TD* __r
         if (d) {
             float sum = to_float(d[i]);
             for (int sp = 1; sp < splits; ++sp) sum += to_float(d[sp * split_stride + i]);
-            if (g) sum *= sigmoid_f(to_float(g[i]));
+            if (g) {
+                float gg = to_float(g[i]);
+                for (int sp = 1; sp < gate_splits; ++sp) gg += to_float(g[sp * gate_split_stride + i]);
+                sum *= sigmoid_f(gg);
+            }
             v += sum;
             if (write_back) r[i] = v;
         }
@@ -280,11 +291,13 @@ __global__ void causal_taps_state_kernel(const T* __restrict__ h, T* __restrict_
 }
 
 // ------------------------------------------ RMS norm of latents + cache write
-// x[t] = [a (na columns) | b (nb columns)], rows `stride` elements apart.  a_out[t] = rmsnorm(a) * wa;
+// x[t] = [a (na columns) | b (nb columns)], rows `stride` elements apart; x may be `splits` float32
+// partial sums `split_stride` elements apart, added in order.  a_out[t] = rmsnorm(a) * wa;
 // rmsnorm(b) * wb goes to cache + slot_map[t] * nb (and nowhere when nb == 0).  One warp per part,
 // two tokens per CTA.
-template <typename T>
-__global__ void latent_norm_store_kernel(const T* __restrict__ x, long long stride, int na, int nb,
+template <typename TI, typename T>
+__global__ void latent_norm_store_kernel(const TI* __restrict__ x, long long stride, int splits,
+                                         long long split_stride, int na, int nb,
                                          const void* __restrict__ wa, const void* __restrict__ wb,
                                          int weight_dtype, float eps, T* __restrict__ a_out,
                                          const int* __restrict__ slot_map, T* __restrict__ cache,
@@ -295,7 +308,7 @@ __global__ void latent_norm_store_kernel(const T* __restrict__ x, long long stri
     const int t = blockIdx.x * (blockDim.x >> 6) + (warp >> 1);      // two warps per token
     const int part = warp & 1;
     if (t >= T_rows || (part == 1 && nb == 0)) return;
-    const T* src = x + static_cast<size_t>(t) * stride + (part == 0 ? 0 : na);
+    const TI* src = x + static_cast<size_t>(t) * stride + (part == 0 ? 0 : na);
     const int n = part == 0 ? na : nb;
     const void* w = part == 0 ? wa : wb;
     T* dst = part == 0 ? a_out + static_cast<size_t>(t) * na
@@ -303,13 +316,23 @@ __global__ void latent_norm_store_kernel(const T* __restrict__ x, long long stri
     float ss = 0.f;
     if (vec4) {
         for (int i = lane * 4; i < n; i += 128) {
-            const F4 v = load4(src + i);
+            F4 v = load4(src + i);
+            for (int sp = 1; sp < splits; ++sp) {
+                const F4 u = load4(src + sp * split_stride + i);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v.v[e] += u.v[e];
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) ss = fmaf(v.v[e], v.v[e], ss);
         }
         const float inv = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(n) + eps);
         for (int i = lane * 4; i < n; i += 128) {
             F4 v = load4(src + i);
+            for (int sp = 1; sp < splits; ++sp) {
+                const F4 u = load4(src + sp * split_stride + i);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v.v[e] += u.v[e];
+            }
             const F4 ww = load4_any(w, weight_dtype, i);
 #pragma unroll
             for (int e = 0; e < 4; ++e) v.v[e] = v.v[e] * inv * ww.v[e];
@@ -318,12 +341,57 @@ __global__ void latent_norm_store_kernel(const T* __restrict__ x, long long stri
         return;
     }
     for (int i = lane; i < n; i += 32) {
-        const float v = to_float(src[i]);
+        float v = to_float(src[i]);
+        for (int sp = 1; sp < splits; ++sp) v += to_float(src[sp * split_stride + i]);
         ss = fmaf(v, v, ss);
     }
     const float inv = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(n) + eps);
-    for (int i = lane; i < n; i += 32)
-        dst[i] = from_float<T>(to_float(src[i]) * inv * load_as_float(w, weight_dtype, i));
+    for (int i = lane; i < n; i += 32) {
+        float v = to_float(src[i]);
+        for (int sp = 1; sp < splits; ++sp) v += to_float(src[sp * split_stride + i]);
+        dst[i] = from_float<T>(v * inv * load_as_float(w, weight_dtype, i));
+    }
+}
+
+// The same for the few rows of a decode step: a CTA per (token, latent), a thread per four
+// columns, so that every load of the row (and of its partial sums) is in flight at once.
+template <typename TI, typename T>
+__global__ void latent_norm_store_wide_kernel(const TI* __restrict__ x, long long stride, int splits,
+                                              long long split_stride, int na, int nb,
+                                              const void* __restrict__ wa,
+                                              const void* __restrict__ wb, int weight_dtype,
+                                              float eps, T* __restrict__ a_out,
+                                              const int* __restrict__ slot_map,
+                                              T* __restrict__ cache) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, part = blockIdx.y;
+    const TI* src = x + static_cast<size_t>(t) * stride + (part == 0 ? 0 : na);
+    const int n = part == 0 ? na : nb;
+    const void* w = part == 0 ? wa : wb;
+    T* dst = part == 0 ? a_out + static_cast<size_t>(t) * na
+                       : cache + static_cast<size_t>(slot_map[t]) * nb;
+    const int i = threadIdx.x * 4;          // n <= 4 * blockDim.x, n a multiple of 4
+    F4 v = F4{{0.f, 0.f, 0.f, 0.f}};
+    if (i < n) {
+        v = load4(src + i);
+        for (int sp = 1; sp < splits; ++sp) {
+            const F4 u = load4(src + sp * split_stride + i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v.v[e] += u.v[e];
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss = fmaf(v.v[e], v.v[e], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(n) + eps);
+    if (i < n) {
+        const F4 ww = load4_any(w, weight_dtype, i);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v.v[e] = v.v[e] * inv * ww.v[e];
+        store4(dst + i, v);
+    }
 }
 
 // ---------------------------------------------------------------- xIELU
@@ -394,16 +462,19 @@ SOMI_API int somi_embed_sinusoid_layernorm(const int* ids, const int* positions,
 
 SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dtype, int delta_splits,
                                 long long delta_split_stride, const void* gate, int gate_dtype,
-                                long long gate_stride, const void* weight, int weight_dtype, float eps,
+                                long long gate_stride, int gate_splits, long long gate_split_stride,
+                                const void* weight, int weight_dtype, float eps,
                                 void* out, int out_dtype, const int* rows, int n_out, int H,
                                 int write_back, int rms, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     if (delta_splits < 1 || (delta_splits > 1 && delta_dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
     if (gate && !delta) return SOMI_ERR_UNSUPPORTED;
+    if (gate_splits < 1 || (gate_splits > 1 && gate_dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(H) * sizeof(float);
     if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
     if (!gate) gate_dtype = out_dtype;
     const int vec4 = (H & 3) == 0 && (gate_stride & 3) == 0 && (delta_split_stride & 3) == 0 &&
+                     (gate_split_stride & 3) == 0 &&
                      ((reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(gate) |
                        reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
     // few rows (a decode step waits for this kernel): a thread per four columns, the row read
@@ -418,17 +489,20 @@ SOMI_API int somi_add_layernorm(float* residual, const void* delta, int delta_dt
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
         launch_pdl(add_layernorm_kernel<TD, TG, TO>, dim3(n_out), dim3(threads), smem,           \
                    stream, residual, static_cast<const TD*>(delta), delta_splits,                \
-                   delta_split_stride, static_cast<const TG*>(gate), gate_stride, weight,        \
+                   delta_split_stride, static_cast<const TG*>(gate), gate_stride, gate_splits,   \
+                   gate_split_stride, weight,                                                    \
                    weight_dtype, eps, static_cast<TO*>(out), rows, H, write_back, rms, vec4);    \
     } while (0)
-    // the gate and the output are of the compute dtype; the delta is that or float32 partial sums
+    // the output is of the compute dtype; the delta and the gate are that or float32 partial sums
     if (out_dtype == SOMI_F32) {
         if (delta_dtype != SOMI_F32 || gate_dtype != SOMI_F32) return SOMI_ERR_UNSUPPORTED;
         SOMI_LAUNCH_LN(float, float, float);
-    } else {
-        if (gate_dtype != SOMI_BF16) return SOMI_ERR_UNSUPPORTED;
+    } else if (gate_dtype == SOMI_BF16) {
         if (delta_dtype == SOMI_F32) SOMI_LAUNCH_LN(float, __nv_bfloat16, __nv_bfloat16);
         else SOMI_LAUNCH_LN(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    } else {     // float32 logits: partial sums of a split-K product
+        if (delta_dtype == SOMI_F32) SOMI_LAUNCH_LN(float, float, __nv_bfloat16);
+        else SOMI_LAUNCH_LN(__nv_bfloat16, float, __nv_bfloat16);
     }
 #undef SOMI_LAUNCH_LN
     return launch_status();
@@ -473,22 +547,40 @@ SOMI_API int somi_causal_taps(const void* h, int dtype, const float* w, void* st
     return launch_status();
 }
 
-SOMI_API int somi_latent_norm_store(const void* x, int dtype, long long stride, int na, int nb,
-                                    const void* wa, const void* wb, int weight_dtype, float eps,
-                                    void* a_out, const int* slot_map, void* cache, int T,
+SOMI_API int somi_latent_norm_store(const void* x, int dtype, long long stride, int splits,
+                                    long long split_stride, int na, int nb, const void* wa,
+                                    const void* wb, int weight_dtype, float eps, void* a_out,
+                                    int out_dtype, const int* slot_map, void* cache, int T,
                                     cudaStream_t stream) {
     if (T <= 0) return 0;
     if (na <= 0 || nb < 0 || (nb > 0 && (!slot_map || !cache))) return SOMI_ERR_UNSUPPORTED;
-    const int vec4 = ((na | nb | static_cast<int>(stride & 3)) & 3) == 0 &&
+    if (splits < 1 || (splits > 1 && dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
+    if (dtype != out_dtype && !(dtype == SOMI_F32 && out_dtype == SOMI_BF16)) return SOMI_ERR_UNSUPPORTED;
+    const int vec4 = ((na | nb | static_cast<int>(stride & 3) | static_cast<int>(split_stride & 3)) & 3) == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a_out) |
                        reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(wa) |
                        reinterpret_cast<uintptr_t>(wb)) & 15) == 0;
-#define SOMI_LAUNCH_LAT(TT)                                                                      \
-    launch_pdl(latent_norm_store_kernel<TT>, dim3((T + 1) / 2), dim3(128), 0, stream,            \
-               static_cast<const TT*>(x), stride, na, nb, wa, wb, weight_dtype, eps,             \
-               static_cast<TT*>(a_out), slot_map, static_cast<TT*>(cache), T, vec4)
-    if (dtype == SOMI_F32) SOMI_LAUNCH_LAT(float);
-    else SOMI_LAUNCH_LAT(__nv_bfloat16);
+#define SOMI_LAUNCH_LAT(TI, TT)                                                                  \
+    launch_pdl(latent_norm_store_kernel<TI, TT>, dim3((T + 1) / 2), dim3(128), 0, stream,        \
+               static_cast<const TI*>(x), stride, splits, split_stride, na, nb, wa, wb,          \
+               weight_dtype, eps, static_cast<TT*>(a_out), slot_map, static_cast<TT*>(cache), T, \
+               vec4)
+    const int widest = max(na, nb);
+    if (vec4 && T <= 64 && widest <= 4096) {
+        const int threads = ((widest / 4 + 31) / 32) * 32;
+#define SOMI_LAUNCH_LATW(TI, TT)                                                                 \
+    launch_pdl(latent_norm_store_wide_kernel<TI, TT>, dim3(T, nb > 0 ? 2 : 1), dim3(threads), 0, \
+               stream, static_cast<const TI*>(x), stride, splits, split_stride, na, nb, wa, wb,  \
+               weight_dtype, eps, static_cast<TT*>(a_out), slot_map, static_cast<TT*>(cache))
+        if (out_dtype == SOMI_F32) SOMI_LAUNCH_LATW(float, float);
+        else if (dtype == SOMI_F32) SOMI_LAUNCH_LATW(float, __nv_bfloat16);
+        else SOMI_LAUNCH_LATW(__nv_bfloat16, __nv_bfloat16);
+#undef SOMI_LAUNCH_LATW
+        return launch_status();
+    }
+    if (out_dtype == SOMI_F32) SOMI_LAUNCH_LAT(float, float);
+    else if (dtype == SOMI_F32) SOMI_LAUNCH_LAT(float, __nv_bfloat16);
+    else SOMI_LAUNCH_LAT(__nv_bfloat16, __nv_bfloat16);
 #undef SOMI_LAUNCH_LAT
     return launch_status();
 }

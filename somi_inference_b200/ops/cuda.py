@@ -444,7 +444,7 @@ class CudaOps:
 
         `delta`: [N, H] in the compute dtype, or float32 [splits, N, H] partial sums added in
         order.  `gate`: logits [N, H] whose rows may lie further apart (a view of a wider
-        product).  With `rows`, only those rows are produced and residual is not written."""
+        product), or float32 [splits, N, H] partial sums.  With `rows`, only those rows are produced and residual is not written."""
         _check(residual, delta, weight, out, rows)
         assert residual.dtype == torch.float32
         H = residual.shape[1]
@@ -453,15 +453,22 @@ class CudaOps:
         if delta is not None and delta.dim() == 3:
             assert delta.dtype == torch.float32
             splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
-        gate_stride = 0
+        gate_stride, gate_splits, gate_split_stride = 0, 1, 0
         if gate is not None:
-            if not gate.is_cuda or gate.stride(1) != 1 or gate.shape != (residual.shape[0], H):
-                raise KernelError("a gate is [rows, H] with contiguous rows")
-            gate_stride = gate.stride(0)
+            if gate.dim() == 3:          # float32 partial sums of a split-K product
+                if not (gate.is_cuda and gate.is_contiguous() and gate.dtype == torch.float32
+                        and tuple(gate.shape[1:]) == (residual.shape[0], H)):
+                    raise KernelError("partial sums of a gate are contiguous float32 [splits, rows, H]")
+                gate_splits, gate_split_stride, gate_stride = gate.shape[0], gate.shape[1] * H, H
+            else:
+                if not gate.is_cuda or gate.stride(1) != 1 or gate.shape != (residual.shape[0], H):
+                    raise KernelError("a gate is [rows, H] with contiguous rows")
+                gate_stride = gate.stride(0)
         rc = self.lib.somi_add_layernorm(
             _ptr(residual), _ptr(delta), _code(delta) if delta is not None else _code(out),
             ctypes.c_int(splits), ctypes.c_longlong(stride), _ptr(gate),
             _code(gate) if gate is not None else _code(out), ctypes.c_longlong(gate_stride),
+            ctypes.c_int(gate_splits), ctypes.c_longlong(gate_split_stride),
             _ptr(weight), _code(weight), ctypes.c_float(eps), _ptr(out), _code(out), _ptr(rows),
             ctypes.c_int(n_out), ctypes.c_int(H), ctypes.c_int(0 if rows is not None else 1),
             ctypes.c_int(1 if rms else 0), self._stream())
@@ -472,7 +479,7 @@ class CudaOps:
             if delta is not None:
                 moved += splits * n * delta.element_size()
             if gate is not None:
-                moved += n * gate.element_size()
+                moved += gate_splits * n * gate.element_size()
             if rows is None:
                 moved += n * 4
             trace.note("add_layernorm", moved, detail=f"splits={splits}" if splits > 1 else "")
@@ -506,19 +513,27 @@ class CudaOps:
 
     def latent_norm_store(self, x, na, nb, wa, wb, eps, a_out, slot_map, cache) -> None:
         """x = [a | b] per row: a_out = rmsnorm(a) * wa; rmsnorm(b) * wb goes to the cache slot of
-        the row's token (`nb` = 0: there is no b)."""
+        the row's token (`nb` = 0: there is no b).  x: [T, na + nb], or float32 [splits, T, na + nb]
+        partial sums that are added up in order."""
         _check(x, wa, wb, a_out, slot_map, cache)
-        assert x.shape[1] == na + nb and a_out.dtype == x.dtype
+        splits, split_stride = 1, 0
+        if x.dim() == 3:                 # float32 partial sums of a split-K product
+            assert x.dtype == torch.float32
+            splits, split_stride = x.shape[0], x.shape[1] * x.shape[2]
+        assert x.shape[-1] == na + nb and (a_out.dtype == x.dtype or x.dtype == torch.float32)
         if nb:
-            assert cache.dtype == x.dtype and cache.shape[-1] == nb and cache.shape[1] == 1
+            assert cache.dtype == a_out.dtype and cache.shape[-1] == nb and cache.shape[1] == 1
             assert wb.dtype == wa.dtype
         rc = self.lib.somi_latent_norm_store(
-            _ptr(x), _code(x), ctypes.c_longlong(x.shape[1]), ctypes.c_int(na), ctypes.c_int(nb),
-            _ptr(wa), _ptr(wb), _code(wa), ctypes.c_float(eps), _ptr(a_out), _ptr(slot_map),
-            _ptr(cache), ctypes.c_int(x.shape[0]), self._stream())
+            _ptr(x), _code(x), ctypes.c_longlong(x.shape[-1]), ctypes.c_int(splits),
+            ctypes.c_longlong(split_stride), ctypes.c_int(na), ctypes.c_int(nb),
+            _ptr(wa), _ptr(wb), _code(wa), ctypes.c_float(eps), _ptr(a_out), _code(a_out),
+            _ptr(slot_map), _ptr(cache), ctypes.c_int(a_out.shape[0]), self._stream())
         self._done(rc, "latent_norm_store")
         if trace.active():
-            trace.note("latent_norm_store", 2 * x.numel() * x.element_size())
+            trace.note("latent_norm_store", x.numel() * x.element_size()
+                       + a_out.shape[0] * (na + nb) * a_out.element_size(),
+                       detail=f"splits={splits}" if splits > 1 else "")
 
     def xielu(self, x, n, act, out) -> None:
         """out[:, :n] = xielu(x[:, :n]) with (p, q) = act; x's rows may be wider than n."""

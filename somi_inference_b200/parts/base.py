@@ -108,7 +108,7 @@ class CacheNeeds:
 class GatedDelta:
     """What a gated residual branch hands to the next norm: the branch's result ([T, H], or
     float32 [splits, T, H] partial sums) and the gate's logits [T, H] (rows may lie further
-    apart than H: a view into a wider product).  The norm adds sigmoid(logits) * delta."""
+    apart than H: a view into a wider product; or float32 partial sums as well).  The norm adds sigmoid(logits) * delta."""
 
     delta: torch.Tensor
     gate_logits: torch.Tensor | None = None

@@ -33,7 +33,10 @@ class SigmoidGate:
         self.proj = Linear(self.weight, self.bias, ctx.ops)
 
     def logits(self, h: torch.Tensor) -> torch.Tensor:
-        return self.proj(h)
+        """[T, out], or (a step of few tokens) the float32 partial sums [splits, T, out] of the
+        split-K product, which the norm's kernel adds up before the sigmoid."""
+        partial = self.proj.partial_sums(h)
+        return partial if partial is not None else self.proj(h)
 
 
 @LAYER_EXTRAS.register("causal_taps")

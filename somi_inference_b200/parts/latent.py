@@ -86,7 +86,9 @@ class LatentAttentionMixer:
         ops, T, H, R = self.ctx.ops, x.shape[0], self.heads, self.kv_rank
         paged = cache.paged
         group = batch.groups[paged.group]
-        lat = self.down(x)                                          # [T, q_rank (+ kv_rank)]
+        lat = self.down.partial_sums(x)           # few tokens: split-K partial sums, added up below
+        if lat is None:
+            lat = self.down(x)                                      # [T, q_rank (+ kv_rank)]
         cq = torch.empty((T, self.q_rank), dtype=x.dtype, device=x.device)
         ops.latent_norm_store(lat, self.q_rank, R if self.own_latent else 0, self.q_norm,
                               self.kv_norm, self.eps, cq,

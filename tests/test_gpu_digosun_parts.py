@@ -101,6 +101,14 @@ def test_gated_residual_layernorm(ops, dtype, splits, gated, T, H):
     few = torch.empty(2, H, dtype=dtype, device="cuda")
     ops.add_layernorm(again, None, None, weight, 1e-5, few, rows)
     assert torch.equal(again, residual) and (few.double() - ref[[2, 1]]).abs().max() < tol(dtype, 1e-5, 3e-2)
+    if gated:     # the gate's logits as partial sums of a split-K product
+        parts = torch.randn(3, T, H, generator=g).cuda()
+        r2 = before.clone()
+        ops.add_layernorm(r2, delta, parts, weight, 1e-5, out)
+        d2 = (delta.double().sum(0) if splits > 1 else delta.double()) * torch.sigmoid(parts.double().sum(0))
+        assert (r2.double() - (before.double() + d2)).abs().max() < 1e-5
+        ref2 = plain.layer_norm(before.double() + d2, weight.double(), 1e-5)
+        assert (out.double() - ref2).abs().max() < tol(dtype, 1e-5, 3e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -135,6 +143,17 @@ def test_latent_norms_and_cache_write(ops, dtype, own, na):
                           batch.groups[0].slot_map if own else None, cache if own else None)
     xd = x.double().cpu()
     assert (out.double().cpu() - plain.rms_norm(xd[:, :na], wa.double().cpu(), 1e-5)).abs().max() < tol(dtype, 1e-5)
+    # the same from float32 partial sums of the projection
+    parts = torch.randn(3, batch.num_tokens, na + nb, generator=g).cuda()
+    out2 = torch.empty_like(out)
+    cache2 = torch.full_like(cache, 7.0)
+    ops.latent_norm_store(parts, na, nb, wa, wb if own else None, 1e-5, out2,
+                          batch.groups[0].slot_map if own else None, cache2 if own else None)
+    pd = parts.double().sum(0).cpu()
+    assert (out2.double().cpu() - plain.rms_norm(pd[:, :na], wa.double().cpu(), 1e-5)).abs().max() < tol(dtype, 1e-5)
+    if own:
+        got = cache2.reshape(-1, 40).double().cpu()[batch.groups[0].slot_map.cpu().long()]
+        assert (got - plain.rms_norm(pd[:, na:], wb.double().cpu(), 1e-5)).abs().max() < tol(dtype, 1e-5)
     flat = cache.reshape(-1, 40).double().cpu()
     slots = batch.groups[0].slot_map.cpu().long()
     if own:
