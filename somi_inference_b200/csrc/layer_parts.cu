@@ -12,8 +12,6 @@
 
 namespace somi {
 
-template <typename T> __device__ __forceinline__ float ld_f(const T* p, size_t i) { return to_float(p[i]); }
-
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 

@@ -10,8 +10,6 @@ Notation: S tokens of one sequence at positions 0..S-1, D the model width, x the
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 
