@@ -28,7 +28,7 @@ constexpr int kGemmBK = 64;               // K per stage: 64 bf16 = one 128-byte
 constexpr int kGemmThreads = 224;
 constexpr int kGemmWBytes = kGemmBN * kGemmBK * 2;      // 16 KiB
 
-enum GemmMode { kGemmBf16 = 0, kGemmF32 = 1, kGemmPartialF32 = 2, kGemmSwiGLU = 3 };
+enum GemmMode { kGemmBf16 = 0, kGemmF32 = 1, kGemmPartialF32 = 2, kGemmSwiGLU = 3, kGemmXieluSide = 4 };
 
 __device__ int g_gemm_error = 0;
 
@@ -77,7 +77,8 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES <= 6 ? 2 : 1))
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                    const __grid_constant__ CUtensorMap x_map, int M, int N, int K,
                    int kb_per_split, int mode, const void* __restrict__ bias, int bias_dtype,
-                   void* __restrict__ out, long long out_split_stride) {
+                   void* __restrict__ out, long long out_split_stride, void* __restrict__ out2,
+                   int n_act, const float* __restrict__ act) {
     // The two MMA threads take the K blocks in turn.  With an even number of stages each stage
     // belongs to one of them for good, and that thread sees every phase of the stage's barrier in
     // order.  With an odd number a stage would alternate between the threads: a thread could meet
@@ -237,6 +238,31 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
 #pragma unroll
                     for (int m = 0; m < TOK; ++m)
                         if (m < M) y[static_cast<size_t>(m) * N + n] = acc[m] + b;
+            } else if (mode == kGemmXieluSide) {
+                // features below n_act: xIELU(acc + bias) to out [M, n_act]; the others (a second
+                // projection that rides on this product): acc + bias to out2 [M, N - n_act].
+                // xIELU with (p, q) = act: z > 0: softplus(p) z^2 + z/2; else
+                // (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, in float32 [constant: act]
+                __nv_bfloat16* y = static_cast<__nv_bfloat16*>(out);
+                __nv_bfloat16* y2 = static_cast<__nv_bfloat16*>(out2);
+                const float p0 = act[0], q0 = act[1];
+                const float ap = fmaxf(p0, 0.f) + log1pf(expf(-fabsf(p0)));
+                const float aq = 0.5f + fmaxf(q0, 0.f) + log1pf(expf(-fabsf(q0)));
+                if (n < N) {
+#pragma unroll
+                    for (int m = 0; m < TOK; ++m) {
+                        if (m >= M) break;
+                        const float z = acc[m] + b;
+                        if (n < n_act) {
+                            // (the result is rounded to bfloat16: the fast exponential is enough)
+                            const float v = z > 0.f ? fmaf(ap * z, z, 0.5f * z)
+                                                    : fmaf(aq, (__expf(z) - 1.0f) - z, 0.5f * z);
+                            y[static_cast<size_t>(m) * n_act + n] = __float2bfloat16_rn(v);
+                        } else {
+                            y2[static_cast<size_t>(m) * (N - n_act) + (n - n_act)] = __float2bfloat16_rn(z);
+                        }
+                    }
+                }
             } else {   // kGemmSwiGLU: even rows of W are gate rows, odd rows the matching up rows
                 __nv_bfloat16* y = static_cast<__nv_bfloat16*>(out);
                 const int half_n = N >> 1;
@@ -266,7 +292,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
 template <int TOK, int STAGES>
 int launch_skinny(const CUtensorMap* w_map, const CUtensorMap* x_map, int M, int N, int K,
                   int splits, int mode, const void* bias, int bias_dtype, void* out,
-                  long long out_split_stride, cudaStream_t stream) {
+                  long long out_split_stride, cudaStream_t stream, void* out2 = nullptr,
+                  int n_act = 0, const float* act = nullptr) {
     constexpr int StageBytes = kGemmWBytes + TOK * kGemmBK * 2;
     const size_t smem = static_cast<size_t>(STAGES) * StageBytes + 1024;
     cudaFuncSetAttribute(skinny_gemm_kernel<TOK, STAGES>,
@@ -275,7 +302,8 @@ int launch_skinny(const CUtensorMap* w_map, const CUtensorMap* x_map, int M, int
     const int kbps = (nkb + splits - 1) / splits;
     dim3 grid((N + kGemmBN - 1) / kGemmBN, (nkb + kbps - 1) / kbps);
     launch_pdl(skinny_gemm_kernel<TOK, STAGES>, dim3(grid), dim3(kGemmThreads), smem, stream, 
-        *w_map, *x_map, M, N, K, kbps, mode, bias, bias_dtype, out, out_split_stride);
+        *w_map, *x_map, M, N, K, kbps, mode, bias, bias_dtype, out, out_split_stride, out2, n_act,
+        act);
     return launch_status();
 }
 
@@ -310,6 +338,11 @@ SOMI_API int somi_gemm_error() {
     return v;
 }
 
+SOMI_API int somi_skinny_gemm_act(const void* w_map, const void* x_map, int x_box_rows, int M, int N,
+                                  int K, int splits, int mode, const void* bias, int bias_dtype,
+                                  void* out, void* out2, int n_act, const float* act,
+                                  int deep_ring, cudaStream_t stream);
+
 // mode: 0 bf16 [M, N]; 1 float32 [M, N]; 2 float32 partial sums [splits, M, N] (bias in split 0);
 // 3 SwiGLU over interleaved gate/up rows, bf16 [M, N / 2].  `x_box_rows` is the box height the
 // x tensor map was made with (16, 32 or 64) and must be >= M.
@@ -317,8 +350,21 @@ SOMI_API int somi_skinny_gemm(const void* w_map, const void* x_map, int x_box_ro
                               int K, int splits, int mode, const void* bias, int bias_dtype,
                               void* out, int deep_ring, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > x_box_rows || K % 8 != 0 || K <= 0 || mode < 0 || mode > 3) return SOMI_ERR_UNSUPPORTED;
+    return somi_skinny_gemm_act(w_map, x_map, x_box_rows, M, N, K, splits, mode, bias, bias_dtype, out,
+                                nullptr, 0, nullptr, deep_ring, stream);
+}
+
+// The same with mode 4: xIELU (its two numbers in `act`, float32) of the first `n_act` features
+// to `out` (bf16 [M, n_act]), the other features, bias added, to `out2` (bf16 [M, N - n_act]).
+SOMI_API int somi_skinny_gemm_act(const void* w_map, const void* x_map, int x_box_rows, int M, int N,
+                                  int K, int splits, int mode, const void* bias, int bias_dtype,
+                                  void* out, void* out2, int n_act, const float* act,
+                                  int deep_ring, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > x_box_rows || K % 8 != 0 || K <= 0 || mode < 0 || mode > 4) return SOMI_ERR_UNSUPPORTED;
     if (mode == kGemmSwiGLU && (N & 1)) return SOMI_ERR_UNSUPPORTED;
+    if (mode == kGemmXieluSide && (!act || n_act < 0 || n_act > N || (n_act < N && !out2)))
+        return SOMI_ERR_UNSUPPORTED;
     if (mode != kGemmPartialF32) splits = 1;
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(w_map);
     const CUtensorMap* xm = static_cast<const CUtensorMap*>(x_map);
@@ -327,7 +373,8 @@ SOMI_API int somi_skinny_gemm(const void* w_map, const void* x_map, int x_box_ro
     // stages each (an even number that fits twice into shared memory), so that one CTA's prologue
     // and epilogue overlap the other's main loop.
 #define SOMI_SKINNY(TOK, ST) \
-    return launch_skinny<TOK, ST>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream)
+    return launch_skinny<TOK, ST>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream, \
+                                  out2, n_act, act)
     switch (x_box_rows) {
         case 16: if (deep_ring) SOMI_SKINNY(16, 8); else SOMI_SKINNY(16, 6);
         case 32: if (deep_ring) SOMI_SKINNY(32, 8); else SOMI_SKINNY(32, 4);

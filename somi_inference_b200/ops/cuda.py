@@ -651,7 +651,7 @@ class CudaOps:
             trace.note("silu_mul", (gu.numel() + out.numel()) * gu.element_size())
 
     # ------------------------------------------------------- tcgen05 matrix product
-    GEMM_BF16, GEMM_F32, GEMM_PARTIAL_F32, GEMM_SWIGLU = 0, 1, 2, 3
+    GEMM_BF16, GEMM_F32, GEMM_PARTIAL_F32, GEMM_SWIGLU, GEMM_XIELU_SIDE = 0, 1, 2, 3, 4
 
     def skinny_splits(self, M: int, N: int, K: int) -> int:
         """How many ranges of K to run side by side: CTAs for about one and a half per SM, at
@@ -696,12 +696,15 @@ class CudaOps:
         return entry[1]
 
     def skinny_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
-                    mode: int = 0, splits: int = 1, deep_ring: bool = False) -> torch.Tensor:
+                    mode: int = 0, splits: int = 1, deep_ring: bool = False,
+                    act: torch.Tensor | None = None, n_act: int = 0):
         """x[M, K] @ w[N, K]^T on tcgen05 tensor cores for M <= 64.
 
         mode GEMM_BF16 -> bf16 [M, N] (+ bias); GEMM_F32 -> float32 [M, N];
         GEMM_PARTIAL_F32 -> float32 [splits', M, N] partial sums over ranges of K (bias in the
-        first); GEMM_SWIGLU -> bf16 [M, N / 2] = silu(even rows) * odd rows of w.
+        first); GEMM_SWIGLU -> bf16 [M, N / 2] = silu(even rows) * odd rows of w;
+        GEMM_XIELU_SIDE -> (bf16 [M, n_act] = xIELU of the first n_act features with the two
+        numbers of `act` (float32), bf16 [M, N - n_act] = the other features), bias added to both.
         """
         _check(x, w, bias)
         M, K = x.shape
@@ -715,22 +718,38 @@ class CudaOps:
             out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         elif mode == self.GEMM_SWIGLU:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        elif mode == self.GEMM_XIELU_SIDE:
+            _check(act)
+            assert act is not None and act.dtype == torch.float32 and act.numel() == 2
+            assert 0 <= n_act <= N
+            out = torch.empty((M, n_act), dtype=torch.bfloat16, device=x.device)
+            out2 = torch.empty((M, N - n_act), dtype=torch.bfloat16, device=x.device)
         else:
             out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         # few CTAs: one per SM with the whole shared memory as an 8-stage ring (a CTA's stream
         # is bound by the bytes it keeps in flight); many CTAs: two per SM with 4 stages each
         ctas = -(-N // 128) * (splits if mode == self.GEMM_PARTIAL_F32 else 1)
         deep_ring = deep_ring or ctas <= 148
-        rc = self.lib.somi_skinny_gemm(
-            ctypes.c_void_p(self._gemm_map(w, 128)), ctypes.c_void_p(self._gemm_map(x, box)),
-            ctypes.c_int(box), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
-            ctypes.c_int(splits), ctypes.c_int(mode), _ptr(bias),
-            _code(bias) if bias is not None else _F32, _ptr(out),
-            ctypes.c_int(1 if deep_ring else 0), self._stream())
+        if mode == self.GEMM_XIELU_SIDE:
+            rc = self.lib.somi_skinny_gemm_act(
+                ctypes.c_void_p(self._gemm_map(w, 128)), ctypes.c_void_p(self._gemm_map(x, box)),
+                ctypes.c_int(box), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                ctypes.c_int(1), ctypes.c_int(mode), _ptr(bias),
+                _code(bias) if bias is not None else _F32, _ptr(out), _ptr(out2),
+                ctypes.c_int(n_act), _ptr(act), ctypes.c_int(1 if deep_ring else 0), self._stream())
+        else:
+            rc = self.lib.somi_skinny_gemm(
+                ctypes.c_void_p(self._gemm_map(w, 128)), ctypes.c_void_p(self._gemm_map(x, box)),
+                ctypes.c_int(box), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                ctypes.c_int(splits), ctypes.c_int(mode), _ptr(bias),
+                _code(bias) if bias is not None else _F32, _ptr(out),
+                ctypes.c_int(1 if deep_ring else 0), self._stream())
         self._done(rc, "skinny_gemm")
         if trace.active():
             trace.note("skinny_gemm", (N * K + M * K) * 2 + out.numel() * out.element_size(),
                        2.0 * M * N * K, detail=f"M={M} N={N} K={K} mode={mode}")
+        if mode == self.GEMM_XIELU_SIDE:
+            return out, out2
         return out
 
     def gemm_f32(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:

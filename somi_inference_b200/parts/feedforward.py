@@ -98,9 +98,14 @@ class DenseFF:
 
     def forward(self, x: torch.Tensor, batch, side: bool = False):
         proj = self._with_side if side else self.up
-        z = proj(x)                                     # [T, inter (+ side)]
-        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        self.ctx.ops.xielu(z, self.inter, self.act, act)
+        fused = proj.xielu_side(x, self.act, self.inter)      # few tokens: in the product's epilogue
+        if fused is not None:
+            act, rest = fused
+        else:
+            z = proj(x)                                 # [T, inter (+ side)]
+            act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+            self.ctx.ops.xielu(z, self.inter, self.act, act)
+            rest = z[:, self.inter:]
         partial = self.down.partial_sums(act)
         y = partial if partial is not None else self.down(act)
-        return (y, z[:, self.inter:]) if side else y
+        return (y, rest) if side else y

@@ -62,6 +62,29 @@ def test_skinny_gemm_swiglu(ops, M, I, K):
     torch.testing.assert_close(y.float(), ref, rtol=1.6e-2, atol=1e-2 * max(ref.abs().max().item(), 1.0))
 
 
+@pytest.mark.parametrize("M,I,side,K", [(8, 4864, 896, 896), (16, 18944, 3584, 3584), (5, 88, 40, 80),
+                                        (3, 200, 0, 64), (1, 77, 131, 136)])
+def test_skinny_gemm_xielu_with_a_side_projection(ops, M, I, side, K):
+    """Features [0, I): xIELU(x W^T + b) with the activation's two numbers; features [I, I + side):
+    x W^T + b as they are (a second projection on the same product)."""
+    from tests.plain import digosun_plain as plain
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(I + side, K, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    b = torch.randn(I + side, generator=g).to(torch.bfloat16).cuda()
+    for p, q in [(0.4, -0.9), (-3.0, 2.0)]:
+        act = torch.tensor([p, q]).cuda()
+        y, rest = ops.skinny_gemm(x, w, b, ops.GEMM_XIELU_SIDE, act=act, n_act=I)
+        ops.check_errors()
+        z = (x.double() @ w.double().T + b.double()).cpu()
+        ref = plain.xielu(z[:, :I], torch.tensor(p).double(), torch.tensor(q).double())
+        assert y.shape == (M, I) and rest.shape == (M, side)
+        torch.testing.assert_close(y.double().cpu(), ref, rtol=1.6e-2, atol=1e-2 * max(ref.abs().max().item(), 1.0))
+        if side:
+            torch.testing.assert_close(rest.double().cpu(), z[:, I:], rtol=1.6e-2,
+                                       atol=1e-2 * max(z.abs().max().item(), 1.0))
+
+
 @pytest.mark.parametrize("M,N,K", [(17, 18992, 896), (17, 896, 896), (8, 18992, 896), (8, 1152, 896),
                                    (64, 18992, 896), (64, 896, 4864), (24, 19000, 2048)])
 def test_skinny_gemm_launched_alone_many_times(ops, M, N, K):
