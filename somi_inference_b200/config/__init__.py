@@ -1,5 +1,7 @@
 """Configuration: typed architecture configs, the model spec they produce, the registry."""
 
+from .dapozen import ARCHITECTURE as DAPOZEN_ARCHITECTURE
+from .dapozen import DapozenConfig
 from .digosun import ARCHITECTURE as DIGOSUN_ARCHITECTURE
 from .digosun import DigosunConfig
 from .qwen2 import ARCHITECTURE as QWEN2_ARCHITECTURE
@@ -10,8 +12,9 @@ from .spec import LayerSpec, ModelSpec, PartSpec, RunSpec
 
 register_architecture(QWEN2_ARCHITECTURE, Qwen2Config)
 register_architecture(DIGOSUN_ARCHITECTURE, DigosunConfig)
+register_architecture(DAPOZEN_ARCHITECTURE, DapozenConfig)
 
 __all__ = ["ConfigError", "Qwen2Config", "QWEN2_ARCHITECTURE", "DigosunConfig",
-           "DIGOSUN_ARCHITECTURE", "LayerSpec", "ModelSpec",
+           "DIGOSUN_ARCHITECTURE", "DapozenConfig", "DAPOZEN_ARCHITECTURE", "LayerSpec", "ModelSpec",
            "PartSpec", "RunSpec", "config_class_for", "load_config",
            "register_architecture", "supported_architectures", "unregister_architecture"]

@@ -1,5 +1,8 @@
-// Causal grouped-query attention over the paged cache, any dtype, any head size
-// (multiple of 16 up to 256), any page size: the reference kernel of the library.
+// Causal grouped-query attention over the paged cache, any dtype, any key and value width up
+// to 256, any page size: the reference kernel of the library.  Which earlier keys a token sees
+// is a parameter: all of them, the last `window`, or those of its own chunk (positions
+// i and j with i / chunk == j / chunk, chunks counted from position 0 of the sequence).  The
+// output may be multiplied by sigmoid(gate) in the epilogue.
 // It is the float32 path's attention and the fallback of the bfloat16 path for
 // sizes that the tensor-core kernels refuse.  Products are accumulated with
 // float32 FMAs, softmax is float32 and online, key tiles are aligned to
@@ -27,15 +30,16 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
                                const int* __restrict__ block_table, int bt_stride,
                                const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                                const int* __restrict__ tiles, int n_tiles, int n_prefill_req,
-                               int n_prefill_tok, int nq, int nkv, int hd, int page_size,
-                               float scale, int window, T* __restrict__ out) {
+                               int n_prefill_tok, int nq, int nkv, int hd, int vd, int page_size,
+                               float scale, int window, int chunk, const T* __restrict__ gate,
+                               long long gate_stride, T* __restrict__ out) {
     extern __shared__ float smem[];
     pdl_launch_dependents();
     pdl_wait();
     float* Qs = smem;                           // [kBM][hd]
     float* Ks = Qs + kBM * hd;                  // [kBN][hd + 1]
-    float* Vs = Ks + kBN * (hd + 1);            // [kBN][hd]
-    float* Ss = Vs + kBN * hd;                  // [kBM][kBN + 1]
+    float* Vs = Ks + kBN * (hd + 1);            // [kBN][vd]
+    float* Ss = Vs + kBN * vd;                  // [kBM][kBN + 1]
     float* m_s = Ss + kBM * (kBN + 1);          // [kBM]
     float* l_s = m_s + kBM;                     // [kBM]
     float* a_s = l_s + kBM;                     // [kBM]
@@ -56,7 +60,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
     const int tid = threadIdx.x;
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;                                   // exclusive
-    const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;   // first key any row reads
+    // first key any row reads
+    const int kv_first = chunk > 0 ? (q_pos0 / chunk) * chunk : (window > 0 ? max(0, q_pos0 - window + 1) : 0);
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
 
     for (int idx = tid; idx < kBM * hd; idx += kThreads) {
@@ -74,22 +79,30 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
         for (int idx = tid; idx < kBN * hd; idx += kThreads) {
             const int n = idx / hd, d = idx - n * hd;
             const int j = kb + n;
-            float kval = 0.f, vval = 0.f;
+            float kval = 0.f;
             if (j >= kv_first && j < kv_end) {
                 const int page = bt[j / page_size];
-                const size_t base = ((static_cast<size_t>(page) * nkv + kvh) * page_size + j % page_size) * hd + d;
-                kval = to_float(kcache[base]);
-                vval = to_float(vcache[base]);
+                kval = to_float(kcache[((static_cast<size_t>(page) * nkv + kvh) * page_size + j % page_size) * hd + d]);
             }
             Ks[n * (hd + 1) + d] = kval;
-            Vs[n * hd + d] = vval;
+        }
+        for (int idx = tid; idx < kBN * vd; idx += kThreads) {
+            const int n = idx / vd, d = idx - n * vd;
+            const int j = kb + n;
+            float vval = 0.f;
+            if (j >= kv_first && j < kv_end) {
+                const int page = bt[j / page_size];
+                vval = to_float(vcache[((static_cast<size_t>(page) * nkv + kvh) * page_size + j % page_size) * vd + d]);
+            }
+            Vs[n * vd + d] = vval;
         }
         __syncthreads();
         for (int idx = tid; idx < kBM * kBN; idx += kThreads) {
             const int m = idx / kBN, n = idx - m * kBN;
             const int j = kb + n, qp = q_pos0 + m;
             float s = -INFINITY;
-            if (m < rows && j <= qp && j >= kv_first && (window <= 0 || j > qp - window)) {
+            if (m < rows && j <= qp && j >= kv_first && (window <= 0 || j > qp - window) &&
+                (chunk <= 0 || j / chunk == qp / chunk)) {
                 s = 0.f;
                 const float* q = Qs + m * hd;
                 const float* k = Ks + n * (hd + 1);
@@ -122,11 +135,11 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
 #pragma unroll
         for (int i = 0; i < kAccPerThread; ++i) {
             const int idx = tid + i * kThreads;
-            if (idx < kBM * hd) {
-                const int m = idx / hd, d = idx - m * hd;
+            if (idx < kBM * vd) {
+                const int m = idx / vd, d = idx - m * vd;
                 float o = acc[i] * a_s[m];
                 const float* p = Ss + m * (kBN + 1);
-                for (int n = 0; n < kBN; ++n) o = fmaf(p[n], Vs[n * hd + d], o);
+                for (int n = 0; n < kBN; ++n) o = fmaf(p[n], Vs[n * vd + d], o);
                 acc[i] = o;
             }
         }
@@ -135,11 +148,16 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
 #pragma unroll
     for (int i = 0; i < kAccPerThread; ++i) {
         const int idx = tid + i * kThreads;
-        if (idx < kBM * hd) {
-            const int m = idx / hd, d = idx - m * hd;
-            if (m < rows)
-                out[static_cast<size_t>(row0 + m) * (nq * hd) + head * hd + d] =
-                    from_float<T>(acc[i] / l_s[m]);
+        if (idx < kBM * vd) {
+            const int m = idx / vd, d = idx - m * vd;
+            if (m < rows) {
+                float o = acc[i] / l_s[m];
+                if (gate != nullptr) {
+                    const float z = to_float(gate[static_cast<size_t>(row0 + m) * gate_stride + head * vd + d]);
+                    o = o / (1.0f + expf(-z));
+                }
+                out[static_cast<size_t>(row0 + m) * (nq * vd) + head * vd + d] = from_float<T>(o);
+            }
         }
     }
 }
@@ -153,12 +171,14 @@ SOMI_API int somi_attention_generic_q_tile() { return kBM; }
 SOMI_API int somi_paged_attention_generic(
     const void* qkv, int dtype, int row_stride, const void* kcache, const void* vcache,
     const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
-    int n_tiles, int n_prefill_req, int n_prefill_tok, int n_decode, int nq, int nkv, int hd,
-    int page_size, float scale, int window, void* out, cudaStream_t stream) {
+    int n_tiles, int n_prefill_req, int n_prefill_tok, int n_decode, int nq, int nkv, int hd, int vd,
+    int page_size, float scale, int window, int chunk, const void* gate, long long gate_stride,
+    void* out, cudaStream_t stream) {
     if (n_tiles + n_decode <= 0) return 0;
-    if (hd <= 0 || hd > kMaxHd || hd % 16 || nkv <= 0 || nq % nkv || page_size <= 0)
+    if (hd <= 0 || hd > kMaxHd || vd <= 0 || vd > kMaxHd || nkv <= 0 || nq % nkv || page_size <= 0 ||
+        (window > 0 && chunk > 0))
         return SOMI_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(kBM) * hd + kBN * (hd + 1) + kBN * hd +
+    const size_t smem = sizeof(float) * (static_cast<size_t>(kBM) * hd + kBN * (hd + 1) + kBN * vd +
                                          kBM * (kBN + 1) + 3 * kBM);
     dim3 grid(n_tiles + n_decode, nq);
 #define SOMI_LAUNCH_ATT(T)                                                                      \
@@ -169,8 +189,8 @@ SOMI_API int somi_paged_attention_generic(
         launch_pdl(paged_attention_generic_kernel<T>, dim3(grid), dim3(kThreads), smem, stream,                     \
             static_cast<const T*>(qkv), row_stride, static_cast<const T*>(kcache),              \
             static_cast<const T*>(vcache), block_table, bt_stride, cu_q, ctx_len, tiles,        \
-            n_tiles, n_prefill_req, n_prefill_tok, nq, nkv, hd, page_size, scale, window,       \
-            static_cast<T*>(out));                                                              \
+            n_tiles, n_prefill_req, n_prefill_tok, nq, nkv, hd, vd, page_size, scale, window,   \
+            chunk, static_cast<const T*>(gate), gate_stride, static_cast<T*>(out));             \
     } while (0)
     if (dtype == SOMI_F32) SOMI_LAUNCH_ATT(float);
     else SOMI_LAUNCH_ATT(__nv_bfloat16);

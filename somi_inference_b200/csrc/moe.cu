@@ -1,0 +1,254 @@
+// Mixture of experts whose routing is a table: token id -> `top` experts.
+//
+//   route:    for every (token, k) pair ("entry" t * top + k) the expert table[id[t], k]; entries are
+//             grouped by expert (a counting sort in one CTA) and the groups are cut into row tiles.
+//   grouped product: one CTA per (row tile of an expert's entries, tile of output columns),
+//             C = A W_e^T with float32 FMAs, every output summed over K in ascending order, so an
+//             entry's result does not depend on the tile it fell into or on the rest of the step.
+//             Epilogues: the experts' gated activation over row-interleaved gate/up weights, or
+//             float32 rows scattered back to the entries' places.
+//   combine:  out[t] = weight * sum_k y[t * top + k] (+ the shared expert's rows), float32.
+//
+// A product over all rows with one weight matrix (a shared expert) is the same kernel with one
+// group.  Everything is decided on the device: the launches depend on the step's layout only.
+#include "common.cuh"
+
+namespace somi {
+
+constexpr int kMoeBM = 32;       // entries per row tile
+constexpr int kMoeBN = 64;       // output columns per CTA
+constexpr int kMoeBK = 32;
+constexpr int kMoeThreads = 256;
+
+// offsets: int32 [E + 1] first sorted position of every expert; sorted: int32 [n_entries] entry
+// ids grouped by expert; tile_expert / tile_row0: int32 [max_tiles], n_tiles: int32 [1].
+__global__ void moe_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, int T,
+                                 int top, int E, int* __restrict__ offsets, int* __restrict__ sorted,
+                                 int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                 int* __restrict__ n_tiles, int max_tiles) {
+    extern __shared__ int sm[];          // counts [E], cursor [E]
+    int* counts = sm;
+    int* cursor = sm + E;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = T * top;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = table[static_cast<size_t>(ids[i / top]) * top + i % top];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = at;
+            cursor[e] = at;
+            for (int r = 0; r < counts[e] && tiles < max_tiles; r += kMoeBM) {
+                tile_expert[tiles] = e;
+                tile_row0[tiles] = at + r;
+                ++tiles;
+            }
+            at += counts[e];
+        }
+        offsets[E] = at;
+        *n_tiles = tiles;
+    }
+    __syncthreads();
+    // one atomic per entry places it in its expert's group; the order inside a group changes no
+    // result (each entry's row is computed by itself)
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = table[static_cast<size_t>(ids[i / top]) * top + i % top];
+        if (e >= 0 && e < E) sorted[atomicAdd(&cursor[e], 1)] = i;
+    }
+}
+
+// MODE 0: out (TO) rows at `scatter` positions (or the sorted position itself), N columns.
+// MODE 1: W's rows alternate gate_j, up_j; g = min(gate, limit), u = clamp(up, -limit, limit);
+//         out[pos, j] = g * sigmoid(alpha * g) * (u + 1), N / 2 columns.
+template <typename T, typename TO, int MODE>
+__global__ void __launch_bounds__(kMoeThreads)
+grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __restrict__ gather,
+                    int gather_div, const T* __restrict__ W, const int* __restrict__ offsets,
+                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                    const int* __restrict__ n_tiles, int n_rows_single, TO* __restrict__ out,
+                    long long out_stride, const int* __restrict__ scatter, int N, int K, float limit,
+                    float alpha) {
+    __shared__ float As[kMoeBK][kMoeBM + 1];
+    __shared__ float Ws[kMoeBK][kMoeBN + 1];
+    __shared__ int rows_s[kMoeBM];
+    pdl_launch_dependents();
+    pdl_wait();
+    int expert = 0, row0, row_end;
+    if (tile_expert != nullptr) {
+        if (static_cast<int>(blockIdx.x) >= *n_tiles) return;
+        expert = tile_expert[blockIdx.x];
+        row0 = tile_row0[blockIdx.x];
+        row_end = offsets[expert + 1];
+    } else {                                   // one group: all rows, weight matrix 0
+        row0 = blockIdx.x * kMoeBM;
+        row_end = n_rows_single;
+        if (row0 >= row_end) return;
+    }
+    const int rows = min(kMoeBM, row_end - row0);
+    const int col0 = blockIdx.y * kMoeBN;
+    const int tid = threadIdx.x;
+    if (tid < kMoeBM) {
+        int src = -1;
+        if (tid < rows) {
+            src = row0 + tid;
+            if (gather != nullptr) src = gather[src] / gather_div;
+        }
+        rows_s[tid] = src;
+    }
+    __syncthreads();
+    const T* Wm = W + static_cast<size_t>(expert) * N * K;
+    const int ty = tid / 16, tx = tid % 16;     // rows ty*2.., columns tx*4..
+    float acc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += kMoeBK) {
+        for (int idx = tid; idx < kMoeBM * kMoeBK; idx += kMoeThreads) {
+            const int m = idx / kMoeBK, kk = idx % kMoeBK;
+            const int src = rows_s[m];
+            As[kk][m] = (src >= 0 && k0 + kk < K)
+                            ? to_float(A[static_cast<size_t>(src) * a_stride + k0 + kk]) : 0.f;
+        }
+        for (int idx = tid; idx < kMoeBN * kMoeBK; idx += kMoeThreads) {
+            const int nn = idx / kMoeBK, kk = idx % kMoeBK;
+            Ws[kk][nn] = (col0 + nn < N && k0 + kk < K)
+                             ? to_float(Wm[static_cast<size_t>(col0 + nn) * K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < kMoeBK; ++kk) {
+            const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float w = Ws[kk][tx * 4 + j];
+                acc[0][j] = fmaf(a0, w, acc[0][j]);
+                acc[1][j] = fmaf(a1, w, acc[1][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = ty * 2 + i;
+        if (m >= rows) continue;
+        const int pos = row0 + m;
+        if (MODE == 0) {
+            const size_t dst = static_cast<size_t>(scatter != nullptr ? scatter[pos] : pos) * out_stride;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = col0 + tx * 4 + j;
+                if (c < N) out[dst + c] = from_float<TO>(acc[i][j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int c = col0 + tx * 4 + j;       // even: a gate row; c + 1 its up row
+                if (c + 1 < N) {
+                    const float g = fminf(acc[i][j], limit);
+                    const float u = fminf(fmaxf(acc[i][j + 1], -limit), limit);
+                    const float y = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+                    out[static_cast<size_t>(pos) * out_stride + c / 2] = from_float<TO>(y);
+                }
+            }
+        }
+    }
+}
+
+// out[t, c] = weight * sum_k y[t * top + k, c] (+ extra[t, c]); float32.
+__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ extra,
+                                   float weight, int top, int H, long long n,
+                                   float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long t = i / H;
+        const int c = static_cast<int>(i - t * H);
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) s += y[(t * top + k) * H + c];
+        s *= weight;
+        if (extra != nullptr) s += extra[i];
+        out[i] = s;
+    }
+}
+
+}  // namespace somi
+
+using namespace somi;
+
+SOMI_API int somi_moe_row_tile() { return kMoeBM; }
+
+// work: int32 [(E + 1) + n_entries + 2 * max_tiles + 1]: offsets, sorted, tile_expert, tile_row0, n_tiles
+SOMI_API int somi_moe_route(const int* ids, const int* table, int T, int top, int E, int* work,
+                            int max_tiles, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (top <= 0 || E <= 0 || E > 4096) return SOMI_ERR_UNSUPPORTED;
+    int* offsets = work;
+    int* sorted = offsets + E + 1;
+    int* tile_expert = sorted + static_cast<size_t>(T) * top;
+    int* tile_row0 = tile_expert + max_tiles;
+    int* n_tiles = tile_row0 + max_tiles;
+    launch_pdl(moe_route_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * E, stream, ids, table, T, top,
+               E, offsets, sorted, tile_expert, tile_row0, n_tiles, max_tiles);
+    return launch_status();
+}
+
+// mode 0: out[scatter ? scatter[pos] : pos] = A W^T rows (out_dtype 0: float32, 1: as A);
+// mode 1: gated activation over interleaved gate/up rows (out as A).  `work` as somi_moe_route
+// left it, or null for one group of `n_rows` rows (the weight is then one matrix).
+SOMI_API int somi_grouped_gemm(const void* A, int dtype, long long a_stride, int gather_div,
+                               int use_gather, const void* W, const int* work, int E, int n_entries,
+                               int max_tiles, int n_rows, void* out, int out_f32,
+                               long long out_stride, int use_scatter, int N, int K, int mode,
+                               float limit, float alpha, cudaStream_t stream) {
+    if (N <= 0 || K <= 0) return SOMI_ERR_UNSUPPORTED;
+    const int* offsets = nullptr; const int* sorted = nullptr; const int* tile_expert = nullptr;
+    const int* tile_row0 = nullptr; const int* n_tiles = nullptr;
+    int tiles;
+    if (work != nullptr) {
+        offsets = work;
+        sorted = offsets + E + 1;
+        tile_expert = sorted + n_entries;
+        tile_row0 = tile_expert + max_tiles;
+        n_tiles = tile_row0 + max_tiles;
+        tiles = max_tiles;
+    } else {
+        tiles = (n_rows + kMoeBM - 1) / kMoeBM;
+    }
+    if (tiles <= 0) return 0;
+    if (mode == 1 && (N & 1)) return SOMI_ERR_UNSUPPORTED;
+    dim3 grid(tiles, (N + kMoeBN - 1) / kMoeBN);
+    const int* gather = use_gather ? sorted : nullptr;
+    const int* scatter = use_scatter ? sorted : nullptr;
+#define SOMI_LAUNCH_GG(TT, TO, MODE)                                                             \
+    launch_pdl(grouped_gemm_kernel<TT, TO, MODE>, grid, dim3(kMoeThreads), 0, stream,            \
+               static_cast<const TT*>(A), a_stride, gather, gather_div, static_cast<const TT*>(W), \
+               offsets, tile_expert, tile_row0, n_tiles, n_rows, static_cast<TO*>(out), out_stride, \
+               scatter, N, K, limit, alpha)
+    if (dtype == SOMI_F32) {
+        if (mode == 1) SOMI_LAUNCH_GG(float, float, 1);
+        else SOMI_LAUNCH_GG(float, float, 0);
+    } else {
+        if (mode == 1) SOMI_LAUNCH_GG(__nv_bfloat16, __nv_bfloat16, 1);
+        else if (out_f32) SOMI_LAUNCH_GG(__nv_bfloat16, float, 0);
+        else SOMI_LAUNCH_GG(__nv_bfloat16, __nv_bfloat16, 0);
+    }
+#undef SOMI_LAUNCH_GG
+    return launch_status();
+}
+
+SOMI_API int somi_moe_combine(const float* y, const float* extra, float weight, int top, int T, int H,
+                              float* out, cudaStream_t stream) {
+    const long long n = static_cast<long long>(T) * H;
+    if (n <= 0) return 0;
+    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+    launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, stream, y, extra, weight, top, H, n, out);
+    return launch_status();
+}

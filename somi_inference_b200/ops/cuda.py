@@ -286,20 +286,30 @@ class CudaOps:
         return moved, flops
 
     def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
-                        out, storage=None) -> None:
+                        out, storage=None, value_dim=None, chunk=None, gate=None) -> None:
         """Attention of every token of the step over the cache (keys/values already stored).
 
         In bfloat16 with head sizes 32/64/128, portions of prompts go to the tensor-core
         prefill kernel and single-token requests to the split-KV kernel (at most 16 query
-        heads per kv head); float32 and every other size go to the generic kernel.
+        heads per kv head); float32 and every other size go to the generic kernel.  So do values
+        of another width than the keys (`value_dim`) and a chunked mask (`chunk`: a token sees
+        the earlier tokens of its own chunk of that many positions).  `gate`: logits [T, nq *
+        value width] (rows may lie further apart); the output is multiplied by their sigmoid.
         """
         _check(qkv, kcache, vcache, out, group.block_table)
         assert kcache.dtype == qkv.dtype
         page_size = kcache.shape[2]
         win = int(window) if window else 0
+        vd = int(value_dim) if value_dim else hd
+        chunk = int(chunk) if chunk else 0
+        if gate is not None and not (gate.is_cuda and gate.dtype == out.dtype and gate.stride(1) == 1
+                                     and gate.shape == out.shape):
+            raise KernelError("an output gate is [T, heads * value width] of the output's dtype "
+                              "with contiguous rows")
         n_decode = batch.num_requests - batch.num_prefill_requests
-        split = n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
-        tensor_core_prefill = (batch.num_prefill_requests > 0
+        plain = vd == hd and chunk == 0         # what the tensor-core kernels compute
+        split = plain and n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
+        tensor_core_prefill = (plain and batch.num_prefill_requests > 0
                                and self.prefill_supported(nq, nkv, hd, qkv.dtype))
         if tensor_core_prefill:
             # Four kernels, the first that takes the sizes: both products on tcgen05 with
@@ -373,8 +383,10 @@ class CudaOps:
                 _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(n_generic_tiles),
                 ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
                 ctypes.c_int(n_generic_decode), ctypes.c_int(nq), ctypes.c_int(nkv),
-                ctypes.c_int(hd), ctypes.c_int(page_size), ctypes.c_float(scale),
-                ctypes.c_int(win), _ptr(out), self._stream())
+                ctypes.c_int(hd), ctypes.c_int(vd), ctypes.c_int(page_size), ctypes.c_float(scale),
+                ctypes.c_int(win), ctypes.c_int(chunk), _ptr(gate),
+                ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
+                self._stream())
             self._done(rc, "paged_attention")
             if trace.active():
                 first = batch.num_prefill_requests if tensor_core_prefill else 0
@@ -422,6 +434,12 @@ class CudaOps:
                                                  batch.num_requests, nq, nkv, hd,
                                                  qkv.element_size(), win),
                            detail="with merge" if max_splits > 1 else "")
+
+        if gate is not None and (tensor_core_prefill or split):
+            # the generic kernel applied the gate to its own rows only
+            first = 0 if tensor_core_prefill else batch.num_prefill_tokens
+            last = batch.num_tokens if split else batch.num_prefill_tokens
+            self.sigmoid_gate_mul(out[first:last], gate[first:last])
 
     # ------------------------------------------------ gated layers, latent attention
     def embed_sinusoid_layernorm(self, ids, positions, table, inv_freq, weight, eps, out) -> None:
@@ -639,6 +657,249 @@ class CudaOps:
             moved, flops = self._attention_work(batch, 0, batch.num_requests, heads, 1, rank,
                                                 q.element_size(), int(window) if window else 0)
             trace.note("latent_attention_generic", moved / 2 + heads * T * rank * q.element_size(), flops)
+
+    # ------------------------------- sandwich norms, convolutions, pair rotation, recurrence
+    def embed_scaled(self, ids, table, scale: float, out) -> None:
+        """out = float32(table[ids]) * scale."""
+        _check(ids, table, out)
+        assert ids.dtype == torch.int32 and out.dtype == torch.float32
+        rc = self.lib.somi_embed_scaled(_ptr(ids), _ptr(table), _code(table), ctypes.c_float(scale),
+                                        _ptr(out), ctypes.c_int(ids.shape[0]),
+                                        ctypes.c_int(table.shape[1]), self._stream())
+        self._done(rc, "embed_scaled")
+        if trace.active():
+            trace.note("embed", ids.shape[0] * table.shape[1] * (table.element_size() + 4))
+
+    def add_normed_rmsnorm(self, residual, delta, weight_b, eps_b, weight, eps, out, rows=None) -> None:
+        """residual += rmsnorm(delta) * weight_b (float32, in place), then, where `out` is given,
+        out = rmsnorm(residual) * weight.  `delta`: [N, H], or float32 [splits, N, H] partial sums
+        added in order, or None (nothing is added).  With `rows`, only those rows are produced and
+        residual is not written."""
+        _check(residual, delta, weight_b, weight, out, rows)
+        assert residual.dtype == torch.float32
+        H = residual.shape[1]
+        n_out = residual.shape[0] if rows is None else rows.shape[0]
+        splits, stride = 1, 0
+        if delta is not None and delta.dim() == 3:
+            assert delta.dtype == torch.float32
+            splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+        rc = self.lib.somi_add_normed_rmsnorm(
+            _ptr(residual), _ptr(delta), _code(delta) if delta is not None else _F32,
+            ctypes.c_int(splits), ctypes.c_longlong(stride), _ptr(weight_b),
+            _code(weight_b) if weight_b is not None else _F32, ctypes.c_float(eps_b), _ptr(weight),
+            _code(weight) if weight is not None else _F32, ctypes.c_float(eps), _ptr(out),
+            _code(out) if out is not None else _F32, _ptr(rows), ctypes.c_int(n_out), ctypes.c_int(H),
+            ctypes.c_int(0 if rows is not None else 1), self._stream())
+        self._done(rc, "add_normed_rmsnorm")
+        if trace.active():
+            n = n_out * H
+            moved = n * 4
+            if out is not None:
+                moved += n * out.element_size()
+            if delta is not None:
+                moved += splits * n * delta.element_size() + (n * 4 if rows is None else 0)
+            trace.note("add_normed_rmsnorm", moved, detail=f"splits={splits}" if splits > 1 else "")
+
+    def check_conv_taps(self, taps: int) -> None:
+        most = int(self.lib.somi_causal_conv_max_taps())
+        if not 1 <= taps <= most:
+            raise KernelError(f"a causal convolution of {taps} taps is not supported (1 to {most})")
+
+    def causal_conv(self, u, channels, weight, bias, state, batch, out, act=None,
+                    add_input=False) -> None:
+        """out[:, :channels] = act(bias + conv(u[:, :channels])) (+ u) over each request's rows.
+        `u` and `out` may be views whose rows are wider than `channels`; `weight`: float32
+        [taps, channels], the newest input's tap last; `state` [slots, taps - 1, channels] holds
+        each request's last inputs and is moved on by this step's rows.  act: None or "silu"."""
+        _check(weight, bias, state)
+        taps = weight.shape[0]
+        if not (u.is_cuda and out.is_cuda and u.stride(1) == 1 and out.stride(1) == 1
+                and u.dtype == out.dtype and u.shape[1] >= channels and out.shape[1] >= channels):
+            raise KernelError("causal_conv takes device tensors with contiguous rows")
+        assert weight.dtype == torch.float32 and weight.shape[1] == channels
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == channels)
+        if taps > 1:
+            assert state is not None and state.dtype == u.dtype
+            assert tuple(state.shape[1:]) == (taps - 1, channels)
+        rc = self.lib.somi_causal_conv(
+            _ptr(u), _code(u), ctypes.c_longlong(u.stride(0)), _ptr(weight), _ptr(bias), _ptr(state),
+            _ptr(batch.cu_q), _ptr(batch.token_request), _ptr(batch.state_slot), _ptr(out),
+            ctypes.c_longlong(out.stride(0)), ctypes.c_int(u.shape[0]),
+            ctypes.c_int(batch.num_requests), ctypes.c_int(channels), ctypes.c_int(taps),
+            ctypes.c_int({None: 0, "silu": 1}[act]), ctypes.c_int(1 if add_input else 0),
+            self._stream())
+        self._done(rc, "causal_conv")
+        if taps > 1:
+            self.launches += 1
+        if trace.active():
+            trace.note("causal_conv", 2 * u.shape[0] * channels * u.element_size()
+                       + 2 * batch.num_requests * (taps - 1) * channels * u.element_size())
+
+    def rotary_pairs_store(self, qkv, positions, inv_freq, nq, nkv, hd, vd, rotary_dim, unit_norm,
+                           eps, slot_map, kcache, vcache) -> None:
+        """Rows of `qkv` hold nq query heads and nkv key heads of `hd` elements, then nkv value
+        heads of `vd`.  Neighbouring pairs (2i, 2i+1) below `rotary_dim` of every query and key
+        head turn by position * inv_freq[i]; with `unit_norm` each head is then divided by its
+        root mean square (eps inside the root).  Queries are rewritten in place; keys and values
+        go to their cache slots (`slot_map` None: nothing is stored)."""
+        _check(positions, inv_freq, slot_map, kcache, vcache)
+        if not (qkv.is_cuda and qkv.stride(1) == 1 and qkv.shape[1] >= (nq + nkv) * hd + nkv * vd):
+            raise KernelError("rotary_pairs_store takes a device tensor with contiguous rows")
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(1, rotary_dim // 2)
+        page_size = 1
+        if slot_map is not None:
+            assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype
+            assert kcache.shape[1] == nkv and kcache.shape[3] == hd and vcache.shape[3] == vd
+            page_size = kcache.shape[2]
+        rc = self.lib.somi_rotary_pairs_store(
+            _ptr(qkv), _code(qkv), ctypes.c_longlong(qkv.stride(0)), _ptr(positions), _ptr(inv_freq),
+            ctypes.c_int(qkv.shape[0]), ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd),
+            ctypes.c_int(vd), ctypes.c_int(rotary_dim), ctypes.c_int(1 if unit_norm else 0),
+            ctypes.c_float(eps), _ptr(slot_map), _ptr(kcache), _ptr(vcache),
+            ctypes.c_int(page_size), self._stream())
+        self._done(rc, "rotary_pairs_store")
+        if trace.active():
+            n = qkv.shape[0] * ((nq + nkv) * hd + nkv * vd)
+            trace.note("rotary_pairs_store", 2 * n * qkv.element_size())
+
+    def sigmoid_gate_mul(self, x, gate) -> None:
+        """x *= sigmoid(gate) (float32 arithmetic); `gate`'s rows may lie further apart."""
+        if not (x.is_cuda and x.is_contiguous() and gate.is_cuda and gate.stride(1) == 1
+                and gate.shape == x.shape and gate.dtype == x.dtype):
+            raise KernelError("sigmoid_gate_mul takes a contiguous x and a gate with contiguous rows")
+        rc = self.lib.somi_sigmoid_gate_mul(_ptr(x), _ptr(gate), _code(x),
+                                            ctypes.c_longlong(gate.stride(0)),
+                                            ctypes.c_longlong(x.shape[0]), ctypes.c_int(x.shape[1]),
+                                            self._stream())
+        self._done(rc, "sigmoid_gate_mul")
+        if trace.active():
+            trace.note("sigmoid_gate_mul", 3 * x.numel() * x.element_size())
+
+    def softcap(self, x, cap: float) -> None:
+        """x = cap * tanh(x / cap), in place (float32)."""
+        _check(x)
+        assert x.dtype == torch.float32
+        rc = self.lib.somi_softcap(_ptr(x), ctypes.c_float(cap), ctypes.c_longlong(x.numel()),
+                                   self._stream())
+        self._done(rc, "softcap")
+        if trace.active():
+            trace.note("softcap", 8 * x.numel())
+
+    def check_ssm_geometry(self, heads: int, groups: int, state: int) -> None:
+        most = int(self.lib.somi_ssm_scan_max_state())
+        if not (1 <= state <= most and groups >= 1 and heads % groups == 0):
+            raise KernelError(f"a state-space mixer with {heads} heads in {groups} groups and a "
+                              f"state of {state} is not supported (state up to {most})")
+
+    def ssm_scan(self, xbc, dt_raw, dt_bias, a_log, skip, state, batch, y, heads, groups, n_state,
+                 vdim) -> None:
+        """The recurrence of a state-space mixer over each request's rows, continued from and
+        left in `state` (float32 [slots, heads, n_state, vdim]); `xbc` rows hold x, B, C; `dt_raw`
+        [T, heads] (a view of wider rows); y: float32 [T, heads * vdim]."""
+        _check(dt_bias, a_log, skip, state, y)
+        if not (xbc.is_cuda and xbc.stride(1) == 1 and dt_raw.is_cuda and dt_raw.stride(1) == 1
+                and dt_raw.dtype == xbc.dtype):
+            raise KernelError("ssm_scan takes device tensors with contiguous rows")
+        assert state.dtype == y.dtype == dt_bias.dtype == a_log.dtype == skip.dtype == torch.float32
+        assert tuple(state.shape[1:]) == (heads, n_state, vdim)
+        assert xbc.shape[1] >= heads * vdim + 2 * groups * n_state
+        rc = self.lib.somi_ssm_scan(
+            _ptr(xbc), _code(xbc), ctypes.c_longlong(xbc.stride(0)), _ptr(dt_raw),
+            ctypes.c_longlong(dt_raw.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state),
+            _ptr(batch.cu_q), _ptr(batch.state_slot), _ptr(y), ctypes.c_int(batch.num_requests),
+            ctypes.c_int(heads), ctypes.c_int(groups), ctypes.c_int(n_state), ctypes.c_int(vdim),
+            self._stream())
+        self._done(rc, "ssm_scan")
+        if trace.active():
+            T = xbc.shape[0]
+            trace.note("ssm_scan", T * (heads * vdim + 2 * groups * n_state) * xbc.element_size()
+                       + T * heads * vdim * 4 + 2 * batch.num_requests * heads * n_state * vdim * 4,
+                       6.0 * T * heads * n_state * vdim)
+
+    def gated_group_rmsnorm(self, y, z, weight, eps, groups, out) -> None:
+        """out = rmsnorm over each of `groups` equal parts of y * silu(z), times weight."""
+        _check(y, weight, out)
+        if not (z.is_cuda and z.stride(1) == 1 and z.shape == y.shape and z.dtype == out.dtype):
+            raise KernelError("gated_group_rmsnorm takes a gate with contiguous rows")
+        assert y.dtype == torch.float32
+        rc = self.lib.somi_gated_group_rmsnorm(
+            _ptr(y), _ptr(z), _code(z), ctypes.c_longlong(z.stride(0)), _ptr(weight), _code(weight),
+            ctypes.c_float(eps), _ptr(out), ctypes.c_int(y.shape[0]), ctypes.c_int(y.shape[1]),
+            ctypes.c_int(groups), self._stream())
+        self._done(rc, "gated_group_rmsnorm")
+        if trace.active():
+            trace.note("gated_group_rmsnorm", y.numel() * (4 + 2 * out.element_size()))
+
+    # ------------------------------------------------------------ mixture of experts
+    def moe_route(self, token_ids, table, num_experts: int) -> tuple[torch.Tensor, int]:
+        """Group the step's (token, k) entries by the expert that `table` [vocab, top] gives each
+        token id.  Returns the device work area that `grouped_product` reads and its tile bound."""
+        _check(token_ids, table)
+        assert token_ids.dtype == torch.int32 and table.dtype == torch.int32
+        T, top = token_ids.shape[0], table.shape[1]
+        bm = int(self.lib.somi_moe_row_tile())
+        max_tiles = -(-T * top // bm) + num_experts
+        work = torch.empty(num_experts + 1 + T * top + 2 * max_tiles + 1, dtype=torch.int32,
+                           device=token_ids.device)
+        rc = self.lib.somi_moe_route(_ptr(token_ids), _ptr(table), ctypes.c_int(T), ctypes.c_int(top),
+                                     ctypes.c_int(num_experts), _ptr(work), ctypes.c_int(max_tiles),
+                                     self._stream())
+        self._done(rc, "moe_route")
+        if trace.active():
+            trace.note("moe_route", 12 * T * top)
+        return work, max_tiles
+
+    def grouped_product(self, a, w, *, route=None, top=1, gather=False, scatter=False,
+                        gated=None, out_float32=False) -> torch.Tensor:
+        """Rows of `a` times the matrix of their group: w [E, N, K].
+
+        `route` = (work, max_tiles) from `moe_route` (None: one group, w [1, N, K], all rows).
+        `gather`: row p of the grouped order reads a[entry(p) // top] (else a[p]); `scatter`: it
+        writes out[entry(p)] (else out[p]).  `gated` = (limit, alpha): w's rows alternate gate,
+        up and the result is g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit),
+        u = clamp(up, -limit, limit), N / 2 columns wide.  Products are float32 FMAs summed over K
+        in ascending order."""
+        _check(a, w)
+        E, N, K = w.shape
+        assert a.shape[1] == K and a.dtype == w.dtype
+        if route is None:
+            assert E == 1
+            work, max_tiles, n_entries, n_rows = None, 0, 0, a.shape[0]
+        else:
+            work, max_tiles = route
+            n_entries = (work.numel() - (E + 1) - 2 * max_tiles - 1)
+            n_rows = n_entries
+        cols = N // 2 if gated is not None else N
+        out_dtype = torch.float32 if (out_float32 and gated is None) else a.dtype
+        out = torch.empty((n_rows, cols), dtype=out_dtype, device=a.device)
+        limit, alpha = gated if gated is not None else (0.0, 0.0)
+        rc = self.lib.somi_grouped_gemm(
+            _ptr(a), _code(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(top),
+            ctypes.c_int(1 if gather else 0), _ptr(w), _ptr(work), ctypes.c_int(E),
+            ctypes.c_int(n_entries), ctypes.c_int(max_tiles), ctypes.c_int(n_rows), _ptr(out),
+            ctypes.c_int(1 if out_dtype == torch.float32 else 0), ctypes.c_longlong(cols),
+            ctypes.c_int(1 if scatter else 0), ctypes.c_int(N), ctypes.c_int(K),
+            ctypes.c_int(1 if gated is not None else 0), ctypes.c_float(limit), ctypes.c_float(alpha),
+            self._stream())
+        self._done(rc, "grouped_product")
+        if trace.active():
+            trace.note("grouped_product", (min(E, n_rows) * N * K + n_rows * K) * a.element_size()
+                       + out.numel() * out.element_size(), 2.0 * n_rows * N * K,
+                       detail=f"E={E} rows={n_rows} N={N} K={K}")
+        return out
+
+    def moe_combine(self, y, extra, weight: float, top: int) -> torch.Tensor:
+        """out[t] = weight * sum_k y[t * top + k] (+ extra[t]); float32."""
+        _check(y, extra)
+        assert y.dtype == torch.float32 and (extra is None or extra.dtype == torch.float32)
+        T, H = y.shape[0] // top, y.shape[1]
+        out = torch.empty((T, H), dtype=torch.float32, device=y.device)
+        rc = self.lib.somi_moe_combine(_ptr(y), _ptr(extra), ctypes.c_float(weight), ctypes.c_int(top),
+                                       ctypes.c_int(T), ctypes.c_int(H), _ptr(out), self._stream())
+        self._done(rc, "moe_combine")
+        if trace.active():
+            trace.note("moe_combine", (y.numel() + out.numel() + (0 if extra is None else extra.numel())) * 4)
+        return out
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
         """out = silu(gate) * up; gate/up are the two halves of `gu`'s rows, or alternate."""

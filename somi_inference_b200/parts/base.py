@@ -26,7 +26,7 @@ Interfaces (duck-typed; the classes below only document them):
                  part the layer does not have is None), with a fourth argument `extras`
                  (name -> built layer extra) where the layer has some; `forward(residual,
                  pending, batch, cache, owns_cache)` returns the delta that the next norm has to
-                 add (a tensor, or a `GatedDelta` for norms that take one).  An arrangement
+                 add (a tensor, or a `GatedDelta` / `NormedDelta` for norms that take one).  An arrangement
                  whose extras keep state per request answers `state_needs() -> StateNeeds`.
 * Layer extra:   whatever its arrangement calls; `declare(params)` and `__init__(params,
                  tensors, ctx)` like every part.
@@ -112,6 +112,17 @@ class GatedDelta:
 
     delta: torch.Tensor
     gate_logits: torch.Tensor | None = None
+
+
+@dataclass
+class NormedDelta:
+    """What a branch with a norm of its own behind it hands to the next norm: the branch's result
+    ([T, H], or float32 [splits, T, H] partial sums) and that norm's weight and eps.  The next
+    norm adds rmsnorm(delta) * weight to the residual stream before it normalises."""
+
+    delta: torch.Tensor
+    weight: torch.Tensor
+    eps: float
 
 
 def names_of(params: Mapping[str, Any]) -> Mapping[str, str]:

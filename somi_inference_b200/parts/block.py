@@ -9,7 +9,7 @@ while normalising, and returns its own feed-forward output as the next `pending`
 
 from __future__ import annotations
 
-from .base import GatedDelta, StateNeeds
+from .base import GatedDelta, NormedDelta, StateNeeds
 from .registry import ARRANGEMENTS
 
 
@@ -31,6 +31,42 @@ class PreNormBlock:
         a = self.mixer.forward(h, batch, cache, owns_cache)
         h = self.feed_forward_norm.forward(residual, a)
         return self.feed_forward.forward(h, batch)
+
+
+@ARRANGEMENTS.register("sandwich_norm")
+class SandwichNormBlock:
+    """A norm before and a norm behind each branch:
+        x = x + norm_b(mixer(norm_a(x)));  x = x + norm_d(feed_forward(norm_c(x)))
+    Norms: `mixer`, `mixer_post`, and with a feed-forward `feed_forward`, `feed_forward_post`.  The
+    post norms must be RMS norms: their weight and eps travel with the branch's result as a
+    `NormedDelta`, and the next norm's kernel normalises the branch, adds it to the residual
+    stream and normalises that, all in float32."""
+
+    def __init__(self, mixer, feed_forward, norms) -> None:
+        if mixer is None:
+            raise ValueError("the sandwich arrangement needs a mixer")
+        want = {"mixer", "mixer_post"}
+        if feed_forward is not None:
+            want |= {"feed_forward", "feed_forward_post"}
+        if set(norms) != want:
+            raise ValueError(f"the sandwich arrangement takes the norms {sorted(want)}, "
+                             f"got {sorted(norms)}")
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = norms["mixer"]
+        self.mixer_post = norms["mixer_post"]
+        self.feed_forward_norm = norms.get("feed_forward")
+        self.feed_forward_post = norms.get("feed_forward_post")
+
+    def forward(self, residual, pending, batch, cache, owns_cache):
+        h = self.mixer_norm.forward(residual, pending)
+        a = self.mixer.forward(h, batch, cache, owns_cache)
+        pending = NormedDelta(a, self.mixer_post.weight, self.mixer_post.eps)
+        if self.feed_forward is None:
+            return pending
+        h = self.feed_forward_norm.forward(residual, pending)
+        f = self.feed_forward.forward(h, batch)
+        return NormedDelta(f, self.feed_forward_post.weight, self.feed_forward_post.eps)
 
 
 @ARRANGEMENTS.register("gated_pre_norm")

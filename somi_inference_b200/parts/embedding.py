@@ -26,12 +26,16 @@ class TokenEmbedding:
         self.ctx = ctx
         self.weight = tensors[names_of(params)["weight"]]
         self.hidden = int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))     # x = E[ids] * scale, in float32
 
     def forward(self, batch) -> torch.Tensor:
         token_ids = batch.token_ids
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32,
                           device=token_ids.device)
-        self.ctx.ops.embed(token_ids, self.weight, out)
+        if self.scale != 1.0:
+            self.ctx.ops.embed_scaled(token_ids, self.weight, self.scale, out)
+        else:
+            self.ctx.ops.embed(token_ids, self.weight, out)
         return out
 
 
@@ -82,6 +86,11 @@ class LMHead:
         n = names_of(params)
         self.ctx = ctx
         self.proj = Linear(tensors[n["tied_to"] if params["tied"] else n["weight"]], None, ctx.ops)
+        # logits <- cap * tanh(logits / cap) where the model has a cap
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.proj.to_float32(h)
+        logits = self.proj.to_float32(h)
+        if self.softcap is not None:
+            self.ctx.ops.softcap(logits, self.softcap)
+        return logits

@@ -1,0 +1,80 @@
+"""Mixture of experts routed by a table: a token's id names its experts.
+
+    experts of token t: table[id_t, 0..top-1] (distinct), each weighted 1 / top
+    expert(h) = W_down (g * sigmoid(alpha * g) * (u + 1)),
+                g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit)
+    y_t = (1 / top) * sum of its experts' outputs (+ a shared expert of the same form, with
+          sizes and limit of its own, that every token passes)
+There is no router product: the step's (token, expert) pairs are grouped by expert on the device
+and every group runs one product against its expert's matrices; gate and up rows are interleaved
+so that the activation is the first product's epilogue.  The weighted sum is float32.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, TensorDecl, names_of
+from .registry import FEED_FORWARDS
+
+
+def _interleave(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[..., ff, K] twice -> [..., 2 ff, K] with rows gate_0, up_0, gate_1, up_1, ..."""
+    return torch.stack([gate, up], dim=-2).reshape(*gate.shape[:-2], 2 * gate.shape[-2], gate.shape[-1])
+
+
+@FEED_FORWARDS.register("table_moe")
+class TableMoE:
+    graph_safe = True
+
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        n = names_of(params)
+        hidden, E, top = int(params["hidden_size"]), int(params["experts"]), int(params["top"])
+        ff = int(params["expert_ff"])
+        decl = [TensorDecl(n["table"], (int(params["vocab_size"]), top), init=f"distinct:{E}",
+                           matrix=False)]
+        for e in range(E):
+            decl += [TensorDecl(n["gate"][e], (ff, hidden)), TensorDecl(n["up"][e], (ff, hidden)),
+                     TensorDecl(n["down"][e], (hidden, ff))]
+        shared = params.get("shared")
+        if shared:
+            sff = int(shared["ff"])
+            decl += [TensorDecl(n["shared_gate"], (sff, hidden)), TensorDecl(n["shared_up"], (sff, hidden)),
+                     TensorDecl(n["shared_down"], (hidden, sff))]
+        return decl
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        n = names_of(params)
+        self.ctx = ctx
+        self.experts, self.top = int(params["experts"]), int(params["top"])
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"top = {self.top} of {self.experts} experts")
+        self.gated = (float(params["limit"]), float(params["alpha"]))
+        self.table = tensors[n["table"]].contiguous()
+        if self.table.numel() and not (0 <= int(self.table.min()) and int(self.table.max()) < self.experts):
+            raise ValueError(f"the routing table names experts outside 0..{self.experts - 1}")
+        E = range(self.experts)
+        self.w_gate_up = _interleave(torch.stack([tensors[n["gate"][e]] for e in E]),
+                                     torch.stack([tensors[n["up"][e]] for e in E])).contiguous()
+        self.w_down = torch.stack([tensors[n["down"][e]] for e in E]).contiguous()
+        shared = params.get("shared")
+        self.shared = None
+        if shared:
+            self.shared = (_interleave(tensors[n["shared_gate"]], tensors[n["shared_up"]])[None].contiguous(),
+                           tensors[n["shared_down"]][None].contiguous(),
+                           (float(shared["limit"]), float(params["alpha"])))
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        ops = self.ctx.ops
+        route = ops.moe_route(batch.token_ids, self.table, self.experts)
+        act = ops.grouped_product(x, self.w_gate_up, route=route, top=self.top, gather=True,
+                                  gated=self.gated)
+        y = ops.grouped_product(act, self.w_down, route=route, top=self.top, scatter=True,
+                                out_float32=True)
+        extra = None
+        if self.shared is not None:
+            w_gu, w_down, gated = self.shared
+            extra = ops.grouped_product(ops.grouped_product(x, w_gu, gated=gated), w_down,
+                                        out_float32=True)
+        return ops.moe_combine(y, extra, 1.0 / self.top, self.top)

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildContext, GatedDelta, TensorDecl, names_of
+from .base import BuildContext, GatedDelta, NormedDelta, TensorDecl, names_of
 from .registry import NORMS
 
 
@@ -29,10 +29,15 @@ class RMSNorm:
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None = None,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
-        """`delta` is [T, size], or float32 [splits, T, size] partial sums that are added up."""
+        """`delta` is [T, size], or float32 [splits, T, size] partial sums that are added up; or a
+        `NormedDelta`: the branch's result passes an RMS norm of its own before it is added."""
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=residual.device)
-        self.ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
+        if isinstance(delta, NormedDelta):
+            self.ctx.ops.add_normed_rmsnorm(residual, delta.delta, delta.weight, delta.eps,
+                                            self.weight, self.eps, out, rows)
+        else:
+            self.ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
         return out
 
 

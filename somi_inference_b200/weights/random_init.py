@@ -33,6 +33,16 @@ def random_tensors(config, seed: int, *, std: float = 0.02,
             t = torch.zeros(decl.shape, dtype=torch.float32)
         elif decl.init == "normal":
             t = torch.empty(decl.shape, dtype=torch.float32).normal_(0.0, std, generator=gen)
+        elif decl.init == "taps":
+            # a short convolution's taps [channels, n]: the newest input passes, older ones count little
+            t = torch.empty(decl.shape, dtype=torch.float32).normal_(0.0, 0.1, generator=gen)
+            t[:, -1] += 1.0
+        elif decl.init.startswith("distinct:"):
+            # an integer table whose rows name distinct members of 0..n-1
+            n = int(decl.init.split(":")[1])
+            rows = [torch.randperm(n, generator=gen)[:decl.shape[1]] for _ in range(decl.shape[0])]
+            out[name] = torch.stack(rows).to(torch.int32)
+            continue
         else:
             raise ValueError(f"tensor {name!r}: unknown init {decl.init!r}")
         out[name] = t.to(dtype)
