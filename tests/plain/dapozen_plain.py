@@ -214,3 +214,11 @@ def forward(cfg: dict, w: dict, tokens, dtype=torch.float64, residuals: list | N
         logits = cap * torch.tanh(logits / cap)
     return logits
 
+
+
+def greedy(cfg: dict, weights: dict, prompt, n_new: int, dtype=torch.float64) -> list[int]:
+    """Greedy continuation by recomputing the whole sequence for every new token."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(forward(cfg, weights, seq, dtype)[-1].argmax()))
+    return seq[len(prompt):]
