@@ -5,6 +5,7 @@
     python bench.py --only decode|prefill|mixed [--shape 0.5b|7b|14b] [--layers L] [--batch B]
                     [--context C] [--prefill-tokens T] [--profile]      one phase (profiling runs)
     python bench.py --arch digosun --only decode|prefill [...]   the same shapes with Digosun layers
+    python bench.py --arch dapozen --only decode|prefill [...]   the same shapes with Dapozen layers
 
 A step is one decode step of the whole engine: 8 requests with 2,048 cached tokens each,
 random bfloat16 weights, one new token per request (batch layout upload, all layers, head,
@@ -56,6 +57,13 @@ DIGOSUN_SHAPES = {
     "14b": dict(q_rank=1536, kv_rank=512, window=1024),
 }
 DIGOSUN_TAPS = 4
+# `--arch dapozen`: the same widths, head counts, head sizes and vocabularies with Dapozen layers in
+# the pattern attention + dense, Mamba-2 + experts, attention + dense, attention + experts:
+# chunked attention (a chunk longer than the timed contexts, so that it reads what the Qwen2 layer
+# reads), four taps on q, k, v, rotation on half of the head; Mamba-2 with an inner width of twice
+# the model's, heads of 64, a state of 128 and four groups; sixteen experts of a quarter of the
+# dense feed-forward's width, two per token, and a shared expert of the same width.
+DAPOZEN = dict(chunk=8192, taps=4, ssm_head=64, ssm_state=128, ssm_groups=4, experts=16, top=2)
 CONTEXT = 2048          # cached tokens per request when decode is timed
 MAX_CONTEXT = 4096      # "benchmark at context 4096": positions the model is laid out for
 LONG_CONTEXT = 40960    # ... when the points at 8 k and 32 k cached tokens are measured too
@@ -209,17 +217,39 @@ def digosun_config(shape: str, layers: int, positions: int) -> dict:
                        for i in range(layers)]}
 
 
-ARCH = "qwen2"     # set by --arch; "digosun" builds the same shapes with the Digosun layer
+def dapozen_config(shape: str, layers: int, positions: int) -> dict:
+    q, z = SHAPES[shape], DAPOZEN
+    D, hd = q["hidden_size"], q["head_dim"]
+    attention = dict(heads=q["num_attention_heads"], kv_heads=q["num_key_value_heads"], dim=hd, vdim=hd,
+                     conv=z["taps"], rot={"dims": hd // 2, "base": q["rope_theta"]}, scale=hd ** -0.5,
+                     mask={"size": z["chunk"]})
+    mamba = dict(heads=2 * D // z["ssm_head"], vdim=z["ssm_head"], state=z["ssm_state"],
+                 groups=z["ssm_groups"], norm_groups=z["ssm_groups"], conv=z["taps"])
+    dense = {"kind": "dense", "ff": q["intermediate_size"]}
+    eff = q["intermediate_size"] // 4
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "shared": {"ff": eff, "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"]}}
+    pattern = [("attention", attention, dense), ("mamba2", mamba, moe), ("attention", attention, dense),
+               ("attention", attention, moe)]
+    return {"architecture": "Dapozen", "vocab": q["vocab_size"], "width": D,
+            "norm": {"eps": q["rms_norm_eps"]}, "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
+            "max_positions": positions,
+            "layers": [dict(zip(("type", "mixer", "mlp"), pattern[i % 4])) for i in range(layers)]}
+
+
+ARCH = "qwen2"     # set by --arch; "digosun" / "dapozen" build the same shapes with their layers
 
 
 def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, positions: int):
     import torch
 
-    from somi_inference_b200.config import DigosunConfig, Qwen2Config
+    from somi_inference_b200.config import DapozenConfig, DigosunConfig, Qwen2Config
     from somi_inference_b200.engine import Engine
     from somi_inference_b200.parts import declared_tensors
     if ARCH == "digosun":
         cfg = DigosunConfig.from_dict(digosun_config(shape, layers, positions))
+    elif ARCH == "dapozen":
+        cfg = DapozenConfig.from_dict(dapozen_config(shape, layers, positions))
     else:
         cfg = Qwen2Config.from_dict(shape_config(shape, layers, positions))
     gen = torch.Generator(device="cuda").manual_seed(0)
@@ -229,6 +259,16 @@ def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, po
             continue
         if d.init == "ones":
             tensors[name] = torch.ones(d.shape, dtype=torch.bfloat16, device="cuda")
+        elif d.init == "zeros":
+            tensors[name] = torch.zeros(d.shape, dtype=torch.bfloat16, device="cuda")
+        elif d.init.startswith("distinct:"):         # a routing table: distinct members of 0..n-1 a row
+            n = int(d.init.split(":")[1])
+            keys = torch.rand((d.shape[0], n), device="cuda", generator=gen)
+            tensors[name] = keys.argsort(dim=1)[:, :d.shape[1]].to(torch.int32).contiguous()
+        elif d.init == "taps":                       # the newest input passes, older ones count little
+            t = torch.empty(d.shape, dtype=torch.float32, device="cuda").normal_(0.0, 0.1, generator=gen)
+            t[:, -1] += 1.0
+            tensors[name] = t.to(torch.bfloat16)
         else:
             t = torch.empty(d.shape, dtype=torch.float32, device="cuda").normal_(0.0, 0.02, generator=gen)
             tensors[name] = t.to(torch.bfloat16)
@@ -260,9 +300,54 @@ def digosun_sizes(cfg) -> dict:
             "window": min((l.mixer.window or 1 << 30) for l in cfg.layers)}
 
 
-def model_sizes(cfg, layers: int) -> dict:
+def dapozen_sizes(cfg, batch: int) -> dict:
+    """The same figures for a Dapozen model.  A decode step of `batch` tokens reads at most
+    batch * top experts of a layer; a Mamba-2 layer reads and writes its float32 state once per
+    request and step; the recurrence's flops are counted with the products (per token)."""
+    D, V = cfg.width, cfg.vocab
+    params = small = kv = pair = state = 0
+    read_params = 0
+    for i in cfg.layer_order():
+        layer = cfg.layers[i]
+        m = layer.mixer
+        if layer.type == "attention":
+            qkv = (m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"]
+            p = (qkv + m["heads"] * m["vdim"]) * D + D * m["heads"] * m["vdim"]
+            small += qkv * (1 + m["conv"])
+            kv += 2 * m["kv_heads"] * (m["dim"] + m["vdim"])
+            pair += 2 * m["heads"] * (m["dim"] + m["vdim"])
+        else:
+            inner = m["heads"] * m["vdim"]
+            conv = inner + 2 * m["groups"] * m["state"]
+            p = (inner + conv + m["heads"]) * D + D * inner + 3 * m["heads"] * m["state"] * m["vdim"]
+            small += conv * (1 + m["conv"]) + inner + 3 * m["heads"]
+            state += 2 * 4 * m["heads"] * m["state"] * m["vdim"]
+        params += p
+        read_params += p
+        small += 4 * D
+        mlp = layer.mlp
+        if mlp is None:
+            continue
+        if mlp["kind"] == "dense":
+            params += 3 * D * mlp["ff"]
+            read_params += 3 * D * mlp["ff"]
+        else:
+            shared = 3 * D * mlp["shared"]["ff"] if mlp.get("shared") else 0
+            one = 3 * D * mlp["expert"]["ff"]
+            params += mlp["router"]["top"] * one + shared
+            read_params += min(mlp["router"]["experts"], batch * mlp["router"]["top"]) * one + shared
+    return {"weight_bytes": 2 * (read_params + small + V * D + D), "kv_bytes_per_token": kv,
+            "matmul_params": params, "head_params": V * D, "attn_flops_per_pair": pair,
+            "state_bytes_per_request": state,
+            "window": min((l.mixer["mask"]["size"] if l.type == "attention" and l.mixer.get("mask")
+                           else 1 << 30) for l in cfg.layers)}
+
+
+def model_sizes(cfg, layers: int, batch: int = 1) -> dict:
     if ARCH == "digosun":
         return digosun_sizes(cfg)
+    if ARCH == "dapozen":
+        return dapozen_sizes(cfg, batch)
     H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     nq, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     per_layer = (nq + 2 * nkv) * hd * H + (nq + 2 * nkv) * hd + nq * hd * H + 3 * H * I + 2 * H
@@ -329,7 +414,7 @@ def time_decode(eng, sampler, reqs, vocab: int, steps: int, warmup: int):
 def decode_roofline(sizes: dict, batch: int, context_mid: float, ms: float, pk: dict, kind: str) -> dict:
     # (a sliding window bounds what a step reads of a request's cache)
     step_bytes = sizes["weight_bytes"] + batch * min(context_mid, sizes.get("window", 1 << 30)) \
-        * sizes["kv_bytes_per_token"]
+        * sizes["kv_bytes_per_token"] + batch * sizes.get("state_bytes_per_request", 0)
     achieved = step_bytes / (ms * 1e-3) / 1e9
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
             "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": kind}
@@ -569,7 +654,7 @@ def run_only(args, pk: dict, kind: str) -> int:
     if args.only == "decode":
         cfg, eng = build_engine(shape, layers, args.batch * (args.context + extra), args.batch + 1,
                                 max(MAX_CONTEXT, args.context + extra))
-        sizes = model_sizes(cfg, layers)
+        sizes = model_sizes(cfg, layers, args.batch)
         sampler = Sampler(eng.ops, eng.device)
         reqs = fill_context(eng, args.batch, cfg.vocab_size, "main", args.context)
         ms, launches, per_step = time_decode(eng, sampler, reqs, cfg.vocab_size, args.steps, args.warmup)
@@ -854,9 +939,10 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--shape", choices=list(SHAPES), default="7b")
-    ap.add_argument("--arch", choices=["qwen2", "digosun"], default="qwen2",
+    ap.add_argument("--arch", choices=["qwen2", "digosun", "dapozen"], default="qwen2",
                     help="with --only decode|prefill: the layer design the shape is built with "
-                         "(digosun: latent attention under a window, gated branches)")
+                         "(digosun: latent attention under a window, gated branches; dapozen: "
+                         "chunked attention with convolutions, Mamba-2 layers, table-routed experts)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true",
@@ -887,7 +973,7 @@ def main() -> int:
     pk, kind = peaks()
     if args.arch != "qwen2":
         if args.only not in ("decode", "prefill"):
-            print("bench.py: --arch digosun goes with --only decode or --only prefill")
+            print(f"bench.py: --arch {args.arch} goes with --only decode or --only prefill")
             return 2
         global ARCH
         ARCH = args.arch

@@ -29,7 +29,7 @@ __device__ __forceinline__ DecodeRange decode_range(int ctx_len, int window) {
     DecodeRange r;
     r.kv_len = ctx_len + 1;                      // the new token's key is already in the cache
     const int pos = ctx_len;
-    r.first_key = window > 0 ? max(0, pos - window + 1) : 0;
+    r.first_key = first_visible_key(pos, window);
     r.first_split = r.first_key / kDecChunk;
     r.n_splits = (r.kv_len + kDecChunk - 1) / kDecChunk;
     return r;

@@ -38,7 +38,7 @@ struct TdRange {
 __device__ __forceinline__ TdRange td_range(int ctx_len, int window) {
     TdRange r;
     r.kv_len = ctx_len + 1;
-    r.first_key = window > 0 ? max(0, ctx_len - window + 1) : 0;
+    r.first_key = first_visible_key(ctx_len, window);
     r.first_split = r.first_key / kTdChunk;
     r.n_splits = (r.kv_len + kTdChunk - 1) / kTdChunk;
     return r;

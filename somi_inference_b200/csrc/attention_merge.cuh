@@ -23,7 +23,7 @@ struct MergeRange {
 // the chunks a request reads: `chunk` keys each, from the window's first key to the newest
 __device__ __forceinline__ MergeRange merge_range(int ctx_len, int window, int chunk) {
     MergeRange r;
-    const int first_key = window > 0 ? max(0, ctx_len - window + 1) : 0;
+    const int first_key = first_visible_key(ctx_len, window);
     r.first_split = first_key / chunk;
     r.n_splits = (ctx_len + 1 + chunk - 1) / chunk;
     return r;

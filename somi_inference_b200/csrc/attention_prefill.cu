@@ -70,7 +70,7 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;
-    const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
+    const int kv_first = first_visible_key(q_pos0, window);
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
 
     for (int c = tid; c < kPfBM * CPR; c += kPfThreads) {
@@ -134,7 +134,7 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                 for (int e = 0; e < 4; ++e) {
                     const int key = kb + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = e < 2 ? pos_lo : pos_hi;
-                    const bool ok = key <= pos && key >= kv_first && (window <= 0 || key > pos - window);
+                    const bool ok = key <= pos && key >= kv_first && key >= first_visible_key(pos, window);
                     const float v = ok ? s[nt][e] * scale_log2e : -INFINITY;
                     s[nt][e] = v;
                     if (e < 2) t_lo = fmaxf(t_lo, v); else t_hi = fmaxf(t_hi, v);

@@ -121,7 +121,7 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
     const int head = rank % nq, kvh = head / (nq / nkv);
     const bool has_b = rows > kPpBM;
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
-    const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
+    const int kv_first = first_visible_key(q_pos0, window);
     const int kb0 = (kv_first / kPpBN) * kPpBN;
     const int end_a = q_pos0 + min(rows, kPpBM), end_all = q_pos0 + rows;
     const int n_a = (end_a - kb0 + kPpBN - 1) / kPpBN;            // key tiles that tile A reads
@@ -281,9 +281,9 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
             const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
             const int tile_pos0 = q_pos0 + x * kPpBM;                // position of the tile's first row
             const int pos = tile_pos0 + row;
-            const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+            const int lo = first_visible_key(pos, window);
             // the highest first visible key among the tile's rows
-            const int lo_max = window > 0 ? max(0, tile_pos0 + kPpBM - 1 - window + 1) : 0;
+            const int lo_max = first_visible_key(tile_pos0 + kPpBM - 1, window);
             const unsigned span = static_cast<unsigned>(pos - lo);
             const int n_x = x == 0 ? n_a : n_t;
             const uint32_t s_addr = tmem_s + x * kPpBN + lane_addr;

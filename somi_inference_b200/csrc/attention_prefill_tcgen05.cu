@@ -198,7 +198,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const int head = rank % nq, kvh = head / (nq / nkv);
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;
-    const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
+    const int kv_first = first_visible_key(q_pos0, window);
     const int kb0 = (kv_first / kFaBN) * kFaBN;
     const int n_tiles = (kv_end - kb0 + kFaBN - 1) / kFaBN;
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
@@ -323,9 +323,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         const int row = q * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const int pos = q_pos0 + row;
-        const int lo = window > 0 ? max(kv_first, pos - window + 1) : kv_first;
+        const int lo = max(kv_first, first_visible_key(pos, window));
         // the highest first visible key among the block's rows, and this row's visible span
-        const int lo_max = window > 0 ? max(kv_first, q_pos0 + kFaBM - 1 - window + 1) : kv_first;
+        const int lo_max = max(kv_first, first_visible_key(q_pos0 + kFaBM - 1, window));
         const unsigned span = static_cast<unsigned>(pos - lo);
         float m = -INFINITY, l = 0.f;        // m: the reference maximum in use (log2 units)
         bool ok = true;

@@ -65,7 +65,7 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     const int head = blockIdx.y, kvh = head / (nq / nkv);
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;
-    const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
+    const int kv_first = first_visible_key(q_pos0, window);
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
 
     for (int c = tid; c < kTpBM * CPR; c += kTpThreads) {
@@ -148,7 +148,7 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
             // tiles that lie wholly inside every row's visible range skip the comparisons
             float t_lo = -INFINITY, t_hi = -INFINITY;
             const bool edge = kb + kTpBN - 1 > q_pos0 + qr || kb < kv_first ||
-                              (window > 0 && kb <= q_pos0 + qr + 15 - window);
+                              (window != 0 && kb < first_visible_key(q_pos0 + qr + 15, window));
             if (edge) {
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt)
@@ -156,7 +156,7 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
                     for (int e = 0; e < 4; ++e) {
                         const int key = kb + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int pos = e < 2 ? pos_lo : pos_hi;
-                        const bool ok = key <= pos && key >= kv_first && (window <= 0 || key > pos - window);
+                        const bool ok = key <= pos && key >= kv_first && key >= first_visible_key(pos, window);
                         const float v = ok ? s[nt][e] * scale_log2e : -INFINITY;
                         s[nt][e] = v;
                         if (e < 2) t_lo = fmaxf(t_lo, v); else t_hi = fmaxf(t_hi, v);

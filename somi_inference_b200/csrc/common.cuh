@@ -73,6 +73,15 @@ __device__ __forceinline__ float rope_hi(float a, float b, float c, float s) {
     return __fmaf_rn(b, c, __fmul_rn(a, s));
 }
 
+// Which earlier keys the token at position `pos` sees, as the first of them (it sees all from
+// there to itself).  window > 0: the last `window` positions, itself included; window < 0: those
+// of its own chunk of -window positions, chunks counted from position 0; 0: all of them.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
 // ---- programmatic dependent launch

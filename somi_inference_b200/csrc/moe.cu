@@ -21,11 +21,12 @@ constexpr int kMoeBK = 32;
 constexpr int kMoeThreads = 256;
 
 // offsets: int32 [E + 1] first sorted position of every expert; sorted: int32 [n_entries] entry
-// ids grouped by expert; tile_expert / tile_row0: int32 [max_tiles], n_tiles: int32 [1].
+// ids grouped by expert; tile_expert / tile_row0: int32 [max_tiles], n_tiles: int32 [1];
+// place: int32 [n_entries] the sorted position of every entry (the inverse of `sorted`).
 __global__ void moe_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, int T,
                                  int top, int E, int* __restrict__ offsets, int* __restrict__ sorted,
                                  int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                                 int* __restrict__ n_tiles, int max_tiles) {
+                                 int* __restrict__ n_tiles, int max_tiles, int* __restrict__ place) {
     extern __shared__ int sm[];          // counts [E], cursor [E]
     int* counts = sm;
     int* cursor = sm + E;
@@ -59,7 +60,106 @@ __global__ void moe_route_kernel(const int* __restrict__ ids, const int* __restr
     // result (each entry's row is computed by itself)
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int e = table[static_cast<size_t>(ids[i / top]) * top + i % top];
-        if (e >= 0 && e < E) sorted[atomicAdd(&cursor[e], 1)] = i;
+        if (e >= 0 && e < E) {
+            const int pos = atomicAdd(&cursor[e], 1);
+            sorted[pos] = i;
+            place[i] = pos;
+        }
+    }
+}
+
+// out[p, :] = a[sorted[p] / top, :]: the rows of the step's tokens in the grouped order.
+template <typename T>
+__global__ void moe_gather_rows_kernel(const T* __restrict__ a, long long a_stride,
+                                       const int* __restrict__ sorted, int top, int K,
+                                       T* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.x;
+    const T* src = a + static_cast<size_t>(sorted[p] / top) * a_stride;
+    T* dst = out + static_cast<size_t>(p) * K;
+    if ((K & 7) == 0 && sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        for (int i = threadIdx.x * 8; i < K; i += blockDim.x * 8)
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+        return;
+    }
+    for (int i = threadIdx.x; i < K; i += blockDim.x) dst[i] = src[i];
+}
+
+// The experts' activation over a product whose columns alternate gate_j, up_j:
+// out[r, j] = g * sigmoid(alpha * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit).
+template <typename T>
+__global__ void clamped_gate_up_kernel(const T* __restrict__ gu, T* __restrict__ out, int ff,
+                                       long long n, float limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float g = fminf(to_float(gu[2 * i]), limit);
+        const float u = fminf(fmaxf(to_float(gu[2 * i + 1]), -limit), limit);
+        out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+// A step of few tokens: every (token, k) entry streams the rows of its own expert.
+// grid (row blocks, entries); a warp computes two weight rows at a time (a gate row and its up
+// row, or two output rows), lanes stride over K with 16-byte loads; x of the entry sits in shared
+// memory as float32.  MODE 1: the gated activation, out [entries, N / 2] bfloat16;
+// MODE 0: out [entries, N] float32.
+constexpr int kGemvWarps = 8;
+constexpr int kGemvRowsPerCta = 64;
+template <int MODE>
+__global__ void __launch_bounds__(kGemvWarps * 32)
+moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int a_div,
+                const __nv_bfloat16* __restrict__ W, const int* __restrict__ ids,
+                const int* __restrict__ table, int top, int E, void* __restrict__ out, int N, int K,
+                float limit, float alpha) {
+    extern __shared__ float xs[];                          // [K]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int entry = blockIdx.y;
+    const int expert = table[static_cast<size_t>(ids[entry / top]) * top + entry % top];
+    if (expert < 0 || expert >= E) return;
+    const __nv_bfloat16* x = A + static_cast<size_t>(entry / a_div) * a_stride;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = __bfloat162float(x[i]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const __nv_bfloat16* Wm = W + static_cast<size_t>(expert) * N * K;
+    const int row_end = min(N, (static_cast<int>(blockIdx.x) + 1) * kGemvRowsPerCta);
+    for (int row = blockIdx.x * kGemvRowsPerCta + warp * 2; row < row_end; row += kGemvWarps * 2) {
+        const __nv_bfloat16* w0 = Wm + static_cast<size_t>(row) * K;
+        const __nv_bfloat16* w1 = w0 + K;
+        const bool two = row + 1 < N;
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll 2
+        for (int k = lane * 8; k < K; k += 256) {
+            const uint4 u0 = *reinterpret_cast<const uint4*>(w0 + k);
+            const uint4 u1 = two ? *reinterpret_cast<const uint4*>(w1 + k) : make_uint4(0, 0, 0, 0);
+            const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&u0);
+            const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&u1);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float x0 = xs[k + 2 * e], x1 = xs[k + 2 * e + 1];
+                a0 = fmaf(__low2float(h0[e]), x0, a0);
+                a0 = fmaf(__high2float(h0[e]), x1, a0);
+                a1 = fmaf(__low2float(h1[e]), x0, a1);
+                a1 = fmaf(__high2float(h1[e]), x1, a1);
+            }
+        }
+        a0 = warp_sum(a0);
+        a1 = warp_sum(a1);
+        if (lane == 0) {
+            if (MODE == 1) {
+                const float g = fminf(a0, limit);
+                const float u = fminf(fmaxf(a1, -limit), limit);
+                static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(entry) * (N / 2) + row / 2] =
+                    __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+            } else {
+                float* o = static_cast<float*>(out) + static_cast<size_t>(entry) * N;
+                o[row] = a0;
+                if (two) o[row + 1] = a1;
+            }
+        }
     }
 }
 
@@ -161,10 +261,12 @@ grouped_gemm_kernel(const T* __restrict__ A, long long a_stride, const int* __re
     }
 }
 
-// out[t, c] = weight * sum_k y[t * top + k, c] (+ extra[t, c]); float32.
-__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ extra,
-                                   float weight, int top, int H, long long n,
-                                   float* __restrict__ out) {
+// out[t, c] = weight * sum_k y[row(t * top + k), c] (+ extra[t, c]); float32.  row(e) = place[e]
+// where the rows of y are in the grouped order, else e.
+template <typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ place,
+                                   const float* __restrict__ extra, float weight, int top, int H,
+                                   long long n, float* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -172,7 +274,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
         const long long t = i / H;
         const int c = static_cast<int>(i - t * H);
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s += y[(t * top + k) * H + c];
+        for (int k = 0; k < top; ++k) {
+            const long long e = t * top + k;
+            s += to_float(y[(place != nullptr ? place[e] : e) * H + c]);
+        }
         s *= weight;
         if (extra != nullptr) s += extra[i];
         out[i] = s;
@@ -185,7 +290,8 @@ using namespace somi;
 
 SOMI_API int somi_moe_row_tile() { return kMoeBM; }
 
-// work: int32 [(E + 1) + n_entries + 2 * max_tiles + 1]: offsets, sorted, tile_expert, tile_row0, n_tiles
+// work: int32 [(E + 1) + n_entries + 2 * max_tiles + 1 + n_entries]: offsets, sorted, tile_expert,
+// tile_row0, n_tiles, place
 SOMI_API int somi_moe_route(const int* ids, const int* table, int T, int top, int E, int* work,
                             int max_tiles, cudaStream_t stream) {
     if (T <= 0) return 0;
@@ -195,8 +301,66 @@ SOMI_API int somi_moe_route(const int* ids, const int* table, int T, int top, in
     int* tile_expert = sorted + static_cast<size_t>(T) * top;
     int* tile_row0 = tile_expert + max_tiles;
     int* n_tiles = tile_row0 + max_tiles;
+    int* place = n_tiles + 1;
     launch_pdl(moe_route_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * E, stream, ids, table, T, top,
-               E, offsets, sorted, tile_expert, tile_row0, n_tiles, max_tiles);
+               E, offsets, sorted, tile_expert, tile_row0, n_tiles, max_tiles, place);
+    return launch_status();
+}
+
+SOMI_API int somi_moe_gather_rows(const void* a, int dtype, long long a_stride, const int* work, int E,
+                                  int n_entries, int top, int K, void* out, cudaStream_t stream) {
+    if (n_entries <= 0) return 0;
+    const int* sorted = work + E + 1;
+    const int threads = min(256, max(32, ((K / 8 + 31) / 32) * 32));
+    if (dtype == SOMI_F32)
+        launch_pdl(moe_gather_rows_kernel<float>, dim3(n_entries), dim3(threads), 0, stream,
+                   static_cast<const float*>(a), a_stride, sorted, top, K, static_cast<float*>(out));
+    else
+        launch_pdl(moe_gather_rows_kernel<__nv_bfloat16>, dim3(n_entries), dim3(threads), 0, stream,
+                   static_cast<const __nv_bfloat16*>(a), a_stride, sorted, top, K,
+                   static_cast<__nv_bfloat16*>(out));
+    return launch_status();
+}
+
+SOMI_API int somi_clamped_gate_up(const void* gu, void* out, int dtype, long long rows, int ff,
+                                  float limit, float alpha, cudaStream_t stream) {
+    const long long n = rows * ff;
+    if (n <= 0) return 0;
+    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+    if (dtype == SOMI_F32)
+        launch_pdl(clamped_gate_up_kernel<float>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const float*>(gu), static_cast<float*>(out), ff, n, limit, alpha);
+    else
+        launch_pdl(clamped_gate_up_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), ff, n,
+                   limit, alpha);
+    return launch_status();
+}
+
+// bfloat16, K a multiple of 8: mode 1 the gated activation (out bfloat16 [entries, N / 2]), mode 0
+// float32 rows [entries, N].  Row e of A is a[e / a_div].
+SOMI_API int somi_moe_gemv(const void* A, long long a_stride, int a_div, const void* W, const int* ids,
+                           const int* table, int top, int E, int n_entries, void* out, int N, int K,
+                           int mode, float limit, float alpha, cudaStream_t stream) {
+    if (n_entries <= 0) return 0;
+    if (K <= 0 || (K & 7) || N <= 0 || (mode == 1 && (N & 1)) || K > 40 * 1024 ||
+        (reinterpret_cast<uintptr_t>(W) & 15))
+        return SOMI_ERR_UNSUPPORTED;
+    dim3 grid((N + kGemvRowsPerCta - 1) / kGemvRowsPerCta, n_entries);
+    const size_t smem = sizeof(float) * K;
+    if (mode == 1) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(moe_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_pdl(moe_gemv_kernel<1>, grid, dim3(kGemvWarps * 32), smem, stream,
+                   static_cast<const __nv_bfloat16*>(A), a_stride, a_div,
+                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(moe_gemv_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_pdl(moe_gemv_kernel<0>, grid, dim3(kGemvWarps * 32), smem, stream,
+                   static_cast<const __nv_bfloat16*>(A), a_stride, a_div,
+                   static_cast<const __nv_bfloat16*>(W), ids, table, top, E, out, N, K, limit, alpha);
+    }
     return launch_status();
 }
 
@@ -244,11 +408,16 @@ SOMI_API int somi_grouped_gemm(const void* A, int dtype, long long a_stride, int
     return launch_status();
 }
 
-SOMI_API int somi_moe_combine(const float* y, const float* extra, float weight, int top, int T, int H,
-                              float* out, cudaStream_t stream) {
+SOMI_API int somi_moe_combine(const void* y, int y_dtype, const int* place, const float* extra,
+                              float weight, int top, int T, int H, float* out, cudaStream_t stream) {
     const long long n = static_cast<long long>(T) * H;
     if (n <= 0) return 0;
     const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
-    launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, stream, y, extra, weight, top, H, n, out);
+    if (y_dtype == SOMI_F32)
+        launch_pdl(moe_combine_kernel<float>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const float*>(y), place, extra, weight, top, H, n, out);
+    else
+        launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                   static_cast<const __nv_bfloat16*>(y), place, extra, weight, top, H, n, out);
     return launch_status();
 }

@@ -236,37 +236,44 @@ __global__ void softcap_kernel(float* __restrict__ x, float cap, long long n) {
 
 // ------------------------------------------------------- state-space recurrence
 // Per request r, head h (group g = h / (heads / groups)) and column p of the head, with a state
-// M [N, P] float32 in the request's slot:
+// M [N, P] float32 in the request's slot (stored [P, N]: a lane's rows n lie side by side):
 //   dt = softplus(dt_raw[t, h] + dt_bias[h]);  M <- exp(-exp(a_log[h]) dt) M + (dt B_t) x_t^T;
 //   y[t, h, p] = sum_n M[n, p] C_t[n] + D[h] x_t[p].
 // x, B, C are columns [0, heads*P), then groups*N, then groups*N of the rows of `xbc`.
 // A CTA owns kScanCols columns of one head of one request and walks through the request's rows
 // of this step; a warp owns kScanColsPerWarp columns, a lane the state rows n = lane + 32 j.
-// The sum over n is a fixed tree (lanes, then j), so y does not depend on how the rows were cut.
+// Rows are staged kScanBlock at a time in shared memory (B, C, the CTA's x columns, dt and the
+// decay, each computed once), the next block's loads in flight while this one is worked on.
+// The sum over n is a fixed tree (j, then lanes), so y does not depend on how the rows were cut.
 constexpr int kScanWarps = 4;
 constexpr int kScanColsPerWarp = 4;
 constexpr int kScanCols = kScanWarps * kScanColsPerWarp;
+constexpr int kScanBlock = 8;
+constexpr int kScanThreads = kScanWarps * 32;
 
 __device__ __forceinline__ float softplus_f(float z) {
     return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.f);
 }
 
 template <typename T, int NPL>
-__global__ void __launch_bounds__(kScanWarps * 32)
+__global__ void __launch_bounds__(kScanThreads)
 ssm_scan_kernel(const T* __restrict__ xbc, long long x_stride, const T* __restrict__ dt_raw,
                 long long dt_stride, const float* __restrict__ dt_bias,
                 const float* __restrict__ a_log, const float* __restrict__ Dskip,
                 float* __restrict__ state, const int* __restrict__ cu_q,
                 const int* __restrict__ state_slot, float* __restrict__ y, int heads, int groups,
                 int N, int P) {
+    extern __shared__ float stage[];                       // [2][kScanBlock][row_f]
+    constexpr int kLoads = (kScanBlock * (64 * NPL + kScanCols + 2) + kScanThreads - 1) / kScanThreads;
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x, h = blockIdx.y;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int p0 = blockIdx.z * kScanCols + warp * kScanColsPerWarp;
-    if (p0 >= P) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cta_p0 = blockIdx.z * kScanCols;
+    const int p0 = cta_p0 + warp * kScanColsPerWarp;
     const int g = h / (heads / groups);
     const int inner = heads * P;
+    const int row_f = 2 * N + kScanCols + 2;               // B, C, x columns, dt, decay
     float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * N * P;
     float m[NPL][kScanColsPerWarp];
 #pragma unroll
@@ -274,44 +281,82 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long x_stride, const T* __restri
 #pragma unroll
         for (int i = 0; i < kScanColsPerWarp; ++i) {
             const int n = lane + 32 * j, p = p0 + i;
-            m[j][i] = (n < N && p < P) ? st[static_cast<size_t>(n) * P + p] : 0.f;
+            m[j][i] = (n < N && p < P) ? st[static_cast<size_t>(p) * N + n] : 0.f;
         }
     const float rate = expf(a_log[h]), bias = dt_bias[h], skip = Dskip[h];
     const int first = cu_q[r], last = cu_q[r + 1];
-    for (int t = first; t < last; ++t) {
+
+    // one staged element: what thread `tid` fetches as its k-th of the block that starts at t0
+    auto fetch = [&](int t0, int k) -> float {
+        const int idx = tid + k * kScanThreads;
+        const int tok = idx / row_f, e = idx - tok * row_f;
+        const int t = t0 + tok;
+        if (tok >= kScanBlock || t >= last) return 0.f;
         const T* row = xbc + static_cast<size_t>(t) * x_stride;
-        const float dt = softplus_f(to_float(dt_raw[static_cast<size_t>(t) * dt_stride + h]) + bias);
-        const float decay = expf(-rate * dt);
-        float xv[kScanColsPerWarp], acc[kScanColsPerWarp];
-#pragma unroll
-        for (int i = 0; i < kScanColsPerWarp; ++i) {
-            xv[i] = p0 + i < P ? to_float(row[static_cast<size_t>(h) * P + p0 + i]) : 0.f;
-            acc[i] = 0.f;
+        if (e < N) return to_float(row[inner + static_cast<size_t>(g) * N + e]);
+        if (e < 2 * N) return to_float(row[inner + static_cast<size_t>(groups + g) * N + (e - N)]);
+        if (e < 2 * N + kScanCols) {
+            const int p = cta_p0 + (e - 2 * N);
+            return p < P ? to_float(row[static_cast<size_t>(h) * P + p]) : 0.f;
         }
+        const float dt = softplus_f(to_float(dt_raw[static_cast<size_t>(t) * dt_stride + h]) + bias);
+        return e == 2 * N + kScanCols ? dt : expf(-rate * dt);
+    };
+    float next[kLoads];
 #pragma unroll
-        for (int j = 0; j < NPL; ++j) {
-            const int n = lane + 32 * j;
-            const float bn = n < N ? to_float(row[inner + static_cast<size_t>(g) * N + n]) * dt : 0.f;
-            const float cn = n < N ? to_float(row[inner + static_cast<size_t>(groups + g) * N + n]) : 0.f;
+    for (int k = 0; k < kLoads; ++k) next[k] = fetch(first, k);
+    int buf = 0;
+    for (int t0 = first; t0 < last; t0 += kScanBlock) {
+        float* cur = stage + buf * kScanBlock * row_f;
 #pragma unroll
-            for (int i = 0; i < kScanColsPerWarp; ++i) {
-                m[j][i] = fmaf(decay, m[j][i], bn * xv[i]);
-                acc[i] = fmaf(m[j][i], cn, acc[i]);
+        for (int k = 0; k < kLoads; ++k) {
+            const int idx = tid + k * kScanThreads;
+            if (idx < kScanBlock * row_f) cur[idx] = next[k];
+        }
+        __syncthreads();
+        if (t0 + kScanBlock < last) {
+#pragma unroll
+            for (int k = 0; k < kLoads; ++k) next[k] = fetch(t0 + kScanBlock, k);
+        }
+        const int n_tok = min(kScanBlock, last - t0);
+        if (p0 < P) {
+            for (int tok = 0; tok < n_tok; ++tok) {
+                const float* row = cur + tok * row_f;
+                const float dt = row[2 * N + kScanCols], decay = row[2 * N + kScanCols + 1];
+                float xv[kScanColsPerWarp], acc[kScanColsPerWarp];
+#pragma unroll
+                for (int i = 0; i < kScanColsPerWarp; ++i) {
+                    xv[i] = row[2 * N + warp * kScanColsPerWarp + i];
+                    acc[i] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < NPL; ++j) {
+                    const int n = lane + 32 * j;
+                    const float bn = n < N ? row[n] * dt : 0.f;
+                    const float cn = n < N ? row[N + n] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < kScanColsPerWarp; ++i) {
+                        m[j][i] = fmaf(decay, m[j][i], bn * xv[i]);
+                        acc[i] = fmaf(m[j][i], cn, acc[i]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kScanColsPerWarp; ++i) {
+                    const float s = warp_sum(acc[i]);
+                    if (lane == 0 && p0 + i < P)
+                        y[static_cast<size_t>(t0 + tok) * inner + static_cast<size_t>(h) * P + p0 + i] =
+                            fmaf(skip, xv[i], s);
+                }
             }
         }
-#pragma unroll
-        for (int i = 0; i < kScanColsPerWarp; ++i) {
-            const float s = warp_sum(acc[i]);
-            if (lane == 0 && p0 + i < P)
-                y[static_cast<size_t>(t) * inner + static_cast<size_t>(h) * P + p0 + i] = fmaf(skip, xv[i], s);
-        }
+        buf ^= 1;       // the block after the next overwrites this buffer only behind the next barrier
     }
 #pragma unroll
     for (int j = 0; j < NPL; ++j)
 #pragma unroll
         for (int i = 0; i < kScanColsPerWarp; ++i) {
             const int n = lane + 32 * j, p = p0 + i;
-            if (n < N && p < P) st[static_cast<size_t>(n) * P + p] = m[j][i];
+            if (n < N && p < P) st[static_cast<size_t>(p) * N + n] = m[j][i];
         }
 }
 
@@ -477,8 +522,9 @@ SOMI_API int somi_ssm_scan(const void* xbc, int dtype, long long x_stride, const
         return SOMI_ERR_UNSUPPORTED;
     dim3 grid(R, heads, (P + kScanCols - 1) / kScanCols);
     const int npl = (N + 31) / 32;
+    const size_t smem = sizeof(float) * 2 * kScanBlock * (2 * N + kScanCols + 2);
 #define SOMI_LAUNCH_SCAN(TT, NPL)                                                                \
-    launch_pdl(ssm_scan_kernel<TT, NPL>, grid, dim3(kScanWarps * 32), 0, stream,                 \
+    launch_pdl(ssm_scan_kernel<TT, NPL>, grid, dim3(kScanThreads), smem, stream,                 \
                static_cast<const TT*>(xbc), x_stride, static_cast<const TT*>(dt_raw), dt_stride, \
                dt_bias, a_log, Dskip, state, cu_q, state_slot, y, heads, groups, N, P)
 #define SOMI_SCAN_BY_N(TT)                                                                       \

@@ -278,7 +278,11 @@ class CudaOps:
             q, c = int(cu[r + 1] - cu[r]), int(ctx[r])
             pairs = q * c + q * (q + 1) // 2
             kv = c + q
-            if window:
+            if window < 0:         # a chunk of -window positions
+                n = -window
+                pairs = sum((c + i) % n + 1 for i in range(q)) if q < 4096 else min(pairs, q * n // 2)
+                kv = min(kv, (c % n) + q)
+            elif window:
                 pairs = sum(min(c + i + 1, window) for i in range(q)) if q < 4096 else min(pairs, q * window)
                 kv = min(kv, window + q - 1)
             moved += 2 * kv * nkv * hd * elt + 2 * q * nq * hd * elt
@@ -307,10 +311,15 @@ class CudaOps:
             raise KernelError("an output gate is [T, heads * value width] of the output's dtype "
                               "with contiguous rows")
         n_decode = batch.num_requests - batch.num_prefill_requests
-        plain = vd == hd and chunk == 0         # what the tensor-core kernels compute
+        plain = vd == hd                        # what the tensor-core kernels compute
+        if chunk and win:
+            raise KernelError("a mask is a window or a chunk, not both")
         split = plain and n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
         tensor_core_prefill = (plain and batch.num_prefill_requests > 0
                                and self.prefill_supported(nq, nkv, hd, qkv.dtype))
+        # the tensor-core kernels take the mask as one number: n > 0 a window, n < 0 a chunk of -n
+        if chunk:
+            win = -chunk
         if tensor_core_prefill:
             # Four kernels, the first that takes the sizes: both products on tcgen05 with
             # accumulators in tensor memory, two query tiles per CTA in ping-pong and the
@@ -384,7 +393,7 @@ class CudaOps:
                 ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
                 ctypes.c_int(n_generic_decode), ctypes.c_int(nq), ctypes.c_int(nkv),
                 ctypes.c_int(hd), ctypes.c_int(vd), ctypes.c_int(page_size), ctypes.c_float(scale),
-                ctypes.c_int(win), ctypes.c_int(chunk), _ptr(gate),
+                ctypes.c_int(max(win, 0)), ctypes.c_int(chunk), _ptr(gate),
                 ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
                 self._stream())
             self._done(rc, "paged_attention")
@@ -794,14 +803,14 @@ class CudaOps:
     def ssm_scan(self, xbc, dt_raw, dt_bias, a_log, skip, state, batch, y, heads, groups, n_state,
                  vdim) -> None:
         """The recurrence of a state-space mixer over each request's rows, continued from and
-        left in `state` (float32 [slots, heads, n_state, vdim]); `xbc` rows hold x, B, C; `dt_raw`
+        left in `state` (float32 [slots, heads, vdim, n_state]); `xbc` rows hold x, B, C; `dt_raw`
         [T, heads] (a view of wider rows); y: float32 [T, heads * vdim]."""
         _check(dt_bias, a_log, skip, state, y)
         if not (xbc.is_cuda and xbc.stride(1) == 1 and dt_raw.is_cuda and dt_raw.stride(1) == 1
                 and dt_raw.dtype == xbc.dtype):
             raise KernelError("ssm_scan takes device tensors with contiguous rows")
         assert state.dtype == y.dtype == dt_bias.dtype == a_log.dtype == skip.dtype == torch.float32
-        assert tuple(state.shape[1:]) == (heads, n_state, vdim)
+        assert tuple(state.shape[1:]) == (heads, vdim, n_state)
         assert xbc.shape[1] >= heads * vdim + 2 * groups * n_state
         rc = self.lib.somi_ssm_scan(
             _ptr(xbc), _code(xbc), ctypes.c_longlong(xbc.stride(0)), _ptr(dt_raw),
@@ -839,7 +848,7 @@ class CudaOps:
         T, top = token_ids.shape[0], table.shape[1]
         bm = int(self.lib.somi_moe_row_tile())
         max_tiles = -(-T * top // bm) + num_experts
-        work = torch.empty(num_experts + 1 + T * top + 2 * max_tiles + 1, dtype=torch.int32,
+        work = torch.empty(num_experts + 1 + 2 * T * top + 2 * max_tiles + 1, dtype=torch.int32,
                            device=token_ids.device)
         rc = self.lib.somi_moe_route(_ptr(token_ids), _ptr(table), ctypes.c_int(T), ctypes.c_int(top),
                                      ctypes.c_int(num_experts), _ptr(work), ctypes.c_int(max_tiles),
@@ -867,7 +876,7 @@ class CudaOps:
             work, max_tiles, n_entries, n_rows = None, 0, 0, a.shape[0]
         else:
             work, max_tiles = route
-            n_entries = (work.numel() - (E + 1) - 2 * max_tiles - 1)
+            n_entries = (work.numel() - (E + 1) - 2 * max_tiles - 1) // 2
             n_rows = n_entries
         cols = N // 2 if gated is not None else N
         out_dtype = torch.float32 if (out_float32 and gated is None) else a.dtype
@@ -888,17 +897,110 @@ class CudaOps:
                        detail=f"E={E} rows={n_rows} N={N} K={K}")
         return out
 
-    def moe_combine(self, y, extra, weight: float, top: int) -> torch.Tensor:
-        """out[t] = weight * sum_k y[t * top + k] (+ extra[t]); float32."""
-        _check(y, extra)
-        assert y.dtype == torch.float32 and (extra is None or extra.dtype == torch.float32)
+    @staticmethod
+    def _route_parts(route, E: int):
+        """(offsets [E + 1], sorted [n], place [n]) views of a work area of `moe_route`."""
+        work, max_tiles = route
+        n = (work.numel() - (E + 1) - 2 * max_tiles - 1) // 2
+        return work[:E + 1], work[E + 1:E + 1 + n], work[work.numel() - n:]
+
+    def moe_gather_rows(self, a, route, E: int, top: int) -> torch.Tensor:
+        """The step's rows in the grouped order: out[p] = a[entry(p) // top]."""
+        _check(a)
+        work, _ = route
+        n = self._route_parts(route, E)[1].numel()
+        out = torch.empty((n, a.shape[1]), dtype=a.dtype, device=a.device)
+        rc = self.lib.somi_moe_gather_rows(_ptr(a), _code(a), ctypes.c_longlong(a.stride(0)), _ptr(work),
+                                           ctypes.c_int(E), ctypes.c_int(n), ctypes.c_int(top),
+                                           ctypes.c_int(a.shape[1]), _ptr(out), self._stream())
+        self._done(rc, "moe_gather_rows")
+        if trace.active():
+            trace.note("moe_gather_rows", 2 * out.numel() * out.element_size())
+        return out
+
+    def clamped_gate_up(self, gu, limit: float, alpha: float) -> torch.Tensor:
+        """Columns of `gu` alternate gate, up: g * sigmoid(alpha * g) * (u + 1) with
+        g = min(gate, limit), u = clamp(up, -limit, limit); float32 arithmetic."""
+        _check(gu)
+        ff = gu.shape[1] // 2
+        out = torch.empty((gu.shape[0], ff), dtype=gu.dtype, device=gu.device)
+        rc = self.lib.somi_clamped_gate_up(_ptr(gu), _ptr(out), _code(gu), ctypes.c_longlong(gu.shape[0]),
+                                           ctypes.c_int(ff), ctypes.c_float(limit), ctypes.c_float(alpha),
+                                           self._stream())
+        self._done(rc, "clamped_gate_up")
+        if trace.active():
+            trace.note("clamped_gate_up", 3 * out.numel() * out.element_size())
+        return out
+
+    def moe_gemv_supported(self, n_entries: int, K: int, dtype) -> bool:
+        """Whether a step's entries are few enough (and the sizes fit) for each to stream its
+        expert's rows by itself."""
+        return dtype == torch.bfloat16 and n_entries <= 64 and K % 8 == 0 and K <= 40 * 1024
+
+    def moe_gemv(self, a, w, token_ids, table, *, per_token: bool, gated=None) -> torch.Tensor:
+        """A step of few tokens: entry e = (token, k) times the matrix of expert
+        table[id[token], k]; w [E, N, K] bfloat16.  `per_token`: a has one row per token (else one
+        per entry).  `gated` = (limit, alpha): rows of w alternate gate, up and the result is the
+        experts' activation, bfloat16 [entries, N / 2]; else float32 [entries, N]."""
+        _check(a, w, token_ids, table)
+        E, N, K = w.shape
+        top = table.shape[1]
+        n = token_ids.shape[0] * top
+        assert a.dtype == w.dtype == torch.bfloat16 and a.shape[1] == K
+        assert a.shape[0] == (token_ids.shape[0] if per_token else n)
+        if gated is not None:
+            out = torch.empty((n, N // 2), dtype=torch.bfloat16, device=a.device)
+        else:
+            out = torch.empty((n, N), dtype=torch.float32, device=a.device)
+        limit, alpha = gated if gated is not None else (0.0, 0.0)
+        rc = self.lib.somi_moe_gemv(
+            _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(top if per_token else 1), _ptr(w),
+            _ptr(token_ids), _ptr(table), ctypes.c_int(top), ctypes.c_int(E), ctypes.c_int(n),
+            _ptr(out), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(1 if gated is not None else 0),
+            ctypes.c_float(limit), ctypes.c_float(alpha), self._stream())
+        self._done(rc, "moe_gemv")
+        if trace.active():
+            trace.note("moe_gemv", (min(E, n) * N * K + n * K) * 2 + out.numel() * out.element_size(),
+                       2.0 * n * N * K, detail=f"E={E} entries={n} N={N} K={K}")
+        return out
+
+    def library_grouped_product(self, a_sorted, w, route) -> torch.Tensor | None:
+        """a_sorted [n, K] (rows in the grouped order) times w [E, N, K] by group, through the
+        library's grouped product (bfloat16, prompt-sized steps); None where this build of the
+        library has none for these sizes (asked once per shape class)."""
+        E, N, K = w.shape
+        if a_sorted.dtype != torch.bfloat16 or K % 8 or N % 8 or not hasattr(torch, "_grouped_mm"):
+            return None
+        if getattr(self, "_grouped_mm_broken", False):
+            return None
+        offsets = self._route_parts(route, E)[0][1:]
+        try:
+            out = torch._grouped_mm(a_sorted, w.transpose(1, 2), offs=offsets)
+        except (RuntimeError, TypeError, NotImplementedError):
+            if torch.cuda.is_current_stream_capturing():
+                raise
+            self._grouped_mm_broken = True
+            return None
+        if trace.active():
+            n = a_sorted.shape[0]
+            trace.note("library_grouped_gemm", (min(E, n) * N * K + n * K + n * N) * 2, 2.0 * n * N * K,
+                       detail=f"E={E} rows={n} N={N} K={K}")
+        return out
+
+    def moe_combine(self, y, extra, weight: float, top: int, place=None) -> torch.Tensor:
+        """out[t] = weight * sum_k y[row(t * top + k)] (+ extra[t]); float32.  `place`: int32, the
+        row of every entry where y's rows are in the grouped order (else row = entry)."""
+        _check(y, extra, place)
+        assert extra is None or extra.dtype == torch.float32
         T, H = y.shape[0] // top, y.shape[1]
         out = torch.empty((T, H), dtype=torch.float32, device=y.device)
-        rc = self.lib.somi_moe_combine(_ptr(y), _ptr(extra), ctypes.c_float(weight), ctypes.c_int(top),
-                                       ctypes.c_int(T), ctypes.c_int(H), _ptr(out), self._stream())
+        rc = self.lib.somi_moe_combine(_ptr(y), _code(y), _ptr(place), _ptr(extra), ctypes.c_float(weight),
+                                       ctypes.c_int(top), ctypes.c_int(T), ctypes.c_int(H), _ptr(out),
+                                       self._stream())
         self._done(rc, "moe_combine")
         if trace.active():
-            trace.note("moe_combine", (y.numel() + out.numel() + (0 if extra is None else extra.numel())) * 4)
+            trace.note("moe_combine", y.numel() * y.element_size()
+                       + (out.numel() + (0 if extra is None else extra.numel())) * 4)
         return out
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:

@@ -67,7 +67,8 @@ class Mamba2Mixer:
         self.out = Linear(tensors[n["o_weight"]], None, ctx.ops)
 
     def cache_needs(self) -> CacheNeeds:
-        state = {self.STATE_SSM: ((self.heads, self.state_size, self.head_dim), torch.float32)}
+        # [heads, head width, state size]: the state's rows of one column lie side by side
+        state = {self.STATE_SSM: ((self.heads, self.head_dim, self.state_size), torch.float32)}
         if self.taps > 1:
             state[self.STATE_CONV] = ((self.taps - 1, self.conv_ch), self.ctx.dtype)
         return CacheNeeds(paged=None, state=StateNeeds(state))

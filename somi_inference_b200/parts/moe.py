@@ -5,9 +5,17 @@
                 g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit)
     y_t = (1 / top) * sum of its experts' outputs (+ a shared expert of the same form, with
           sizes and limit of its own, that every token passes)
-There is no router product: the step's (token, expert) pairs are grouped by expert on the device
-and every group runs one product against its expert's matrices; gate and up rows are interleaved
-so that the activation is the first product's epilogue.  The weighted sum is float32.
+There is no router product.  Gate and up rows are interleaved, so that the activation can be a
+product's epilogue.  Three ways through the routed experts, by the step's size and dtype:
+  * few (token, expert) pairs, bfloat16: every pair streams the rows of its own expert (a
+    matrix-vector kernel; nothing is sorted);
+  * many pairs, bfloat16: the pairs are grouped by expert on the device, the rows gathered in that
+    order, and the library's grouped product runs over them, as the engine's prompt-sized products
+    run in the library; the activation is a kernel between the two products;
+  * float32, and sizes the others refuse: the engine's own grouped product (float32 FMAs, every
+    output summed over K in ascending order whatever the step).
+The shared expert is two ordinary products with the activation's kernel between them.  The
+weighted sum is float32.
 """
 
 from __future__ import annotations
@@ -15,6 +23,7 @@ from __future__ import annotations
 import torch
 
 from .base import BuildContext, TensorDecl, names_of
+from .linear import Linear
 from .registry import FEED_FORWARDS
 
 
@@ -61,20 +70,31 @@ class TableMoE:
         shared = params.get("shared")
         self.shared = None
         if shared:
-            self.shared = (_interleave(tensors[n["shared_gate"]], tensors[n["shared_up"]])[None].contiguous(),
-                           tensors[n["shared_down"]][None].contiguous(),
+            self.shared = (Linear(_interleave(tensors[n["shared_gate"]], tensors[n["shared_up"]]).contiguous(),
+                                  None, ctx.ops),
+                           Linear(tensors[n["shared_down"]], None, ctx.ops),
                            (float(shared["limit"]), float(params["alpha"])))
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
-        ops = self.ctx.ops
-        route = ops.moe_route(batch.token_ids, self.table, self.experts)
-        act = ops.grouped_product(x, self.w_gate_up, route=route, top=self.top, gather=True,
-                                  gated=self.gated)
-        y = ops.grouped_product(act, self.w_down, route=route, top=self.top, scatter=True,
-                                out_float32=True)
+        ops, top, E = self.ctx.ops, self.top, self.experts
         extra = None
         if self.shared is not None:
-            w_gu, w_down, gated = self.shared
-            extra = ops.grouped_product(ops.grouped_product(x, w_gu, gated=gated), w_down,
-                                        out_float32=True)
-        return ops.moe_combine(y, extra, 1.0 / self.top, self.top)
+            gate_up, down, (limit, alpha) = self.shared
+            extra = down.to_float32(ops.clamped_gate_up(gate_up(x), limit, alpha))
+        n_entries = x.shape[0] * top
+        if ops.moe_gemv_supported(n_entries, x.shape[1], x.dtype) and self.w_down.shape[2] % 8 == 0:
+            act = ops.moe_gemv(x, self.w_gate_up, batch.token_ids, self.table, per_token=True,
+                               gated=self.gated)
+            y = ops.moe_gemv(act, self.w_down, batch.token_ids, self.table, per_token=False)
+            return ops.moe_combine(y, extra, 1.0 / top, top)
+        route = ops.moe_route(batch.token_ids, self.table, E)
+        if x.dtype == torch.bfloat16:
+            rows = ops.moe_gather_rows(x, route, E, top)
+            gu = ops.library_grouped_product(rows, self.w_gate_up, route)
+            if gu is not None:
+                y = ops.library_grouped_product(ops.clamped_gate_up(gu, *self.gated), self.w_down, route)
+                if y is not None:
+                    return ops.moe_combine(y, extra, 1.0 / top, top, place=ops._route_parts(route, E)[2])
+        act = ops.grouped_product(x, self.w_gate_up, route=route, top=top, gather=True, gated=self.gated)
+        y = ops.grouped_product(act, self.w_down, route=route, top=top, scatter=True, out_float32=True)
+        return ops.moe_combine(y, extra, 1.0 / top, top)

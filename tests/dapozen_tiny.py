@@ -8,6 +8,8 @@ B: an odd width, one head everywhere, key and value widths that are no multiple 
    longer than any test sequence, no loop, no soft cap, one norm group over everything.
 C: keys and values of equal width (one cache tensor), a chunk of 64 over pages of 16, a loop run
    three times, three of eight experts, five taps, rotation on the whole head.
+D: head sizes of 64 and 128, which the tensor-core attention kernels take in bfloat16, under
+   chunks (48, 200) that are no multiple of a key tile, a page or a query tile.
 """
 
 from __future__ import annotations
@@ -61,8 +63,13 @@ TINY_C = dict(architecture="Dapozen", vocab=257, width=96, norm={"eps": 1e-6}, e
               layers=[layer("mamba2", mamba(8, 8, 16, 4, 2, 5), moe(8, 3, 32, 1.0, shared=(48, 1.0))),
                       layer("attention", attention(4, 2, 32, 32, 5, 0.5, 64, rot=(32, 1e6)), dense(160)),
                       layer("attention", attention(6, 6, 16, 24, 2, 0.75, 16, rot=(4, 100.0)), moe(4, 1, 40, 4.0))])
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-PAGE_SIZES = {"A": 8, "B": 4, "C": 16}
+TINY_D = dict(architecture="Dapozen", vocab=300, width=128, norm={"eps": 1e-6}, embedding={"scale": 2.0},
+              logit_softcap=15.0,
+              layers=[layer("attention", attention(4, 2, 64, 64, 2, 0.3, 48, rot=(32, 1e4)), dense(256)),
+                      layer("mamba2", mamba(4, 16, 32, 2, 2, 4), moe(4, 2, 64, 2.0)),
+                      layer("attention", attention(2, 1, 128, 128, 3, 0.2, 200, rot=(128, 1e4)), dense(192))])
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+PAGE_SIZES = {"A": 8, "B": 4, "C": 16, "D": 16}
 
 
 def random_weights(raw: dict, seed: int, dtype=torch.float32) -> dict[str, torch.Tensor]:

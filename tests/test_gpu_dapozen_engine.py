@@ -2,7 +2,7 @@
 work: whole prompts; most of a prompt and then token by token; portions of changing size down to
 two tokens; up to four live requests in one batch with so few pages and slots that both are
 used again; long decoding past every chunk; greedy generation through `LLM` and the command
-line.  float32 and bfloat16, three small configurations (tests/dapozen_tiny.py)."""
+line.  float32 and bfloat16, four small configurations (tests/dapozen_tiny.py)."""
 
 import json
 import os
@@ -19,7 +19,7 @@ from tests.plain import dapozen_plain as plain
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 97, 40, 70, 1, 33, 100, 64, 81, 2], "B": [3, 50, 17, 64, 1, 30],
-           "C": [150, 5, 129, 71, 200, 16, 90]}
+           "C": [150, 5, 129, 71, 200, 16, 90], "D": [300, 70, 1, 180, 33, 257]}
 # float32: logits are of size 3-8 here; bfloat16: every activation between two kernels is rounded
 # to 8 bits.  A wrong key, a chunk that is off by one or a lost state moves a logit by its own size.
 ATOL = {"float32": lambda s: 4e-5 * max(1.0, s), "bfloat16": lambda s: 8e-2 * s}

@@ -212,7 +212,9 @@ def gather_cache(view, table_row, length, page_size):
 @pytest.mark.parametrize("case", [
     # (heads, kv heads, key width, value width, chunk, page size)
     (4, 2, 12, 20, 9, 8), (2, 1, 16, 16, 21, 4), (3, 3, 5, 3, 1, 4), (2, 2, 32, 8, 64, 16),
-    (1, 1, 40, 40, 300, 16)])
+    (1, 1, 40, 40, 300, 16),
+    # head sizes of the tensor-core kernels (bfloat16): the same mask as one signed number
+    (4, 2, 64, 64, 96, 16), (8, 1, 128, 128, 300, 16), (4, 4, 128, 128, 50, 8)])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_chunked_attention_with_planted_keys(ops, dtype, case):
     """Prompt portions and single tokens whose queries point at one scaled key each: the chunk's
@@ -220,10 +222,10 @@ def test_chunked_attention_with_planted_keys(ops, dtype, case):
     back, the token itself."""
     nq, nkv, hd, vd, chunk, ps = case
     g = torch.Generator().manual_seed(chunk)
-    steps = Steps(ops, 5, paged=PagedKVNeeds(nkv, hd, chunk, vd if vd != hd else None), dtype=dtype,
+    steps = Steps(ops, 6, paged=PagedKVNeeds(nkv, hd, chunk, vd if vd != hd else None), dtype=dtype,
                   page_size=ps, max_len=400)
     steps.step({"a": 130, "b": 2 * chunk + 3 if chunk < 100 else 77, "c": 1, "d": chunk})
-    batch, where = steps.step({"a": 19, "b": 1, "c": 2, "d": 1, "e": 37})
+    batch, where = steps.step({"a": 19, "b": 1, "c": 2, "d": 1, "e": 37, "f": 290})
     view = steps.mgr.view(0).paged
     for t in (view.keys, view.values):
         t.copy_(torch.randn(t.shape, generator=g).to(dtype))
@@ -243,17 +245,28 @@ def test_chunked_attention_with_planted_keys(ops, dtype, case):
             if page < 0:          # given back: it lies before the chunk and must not be read anyway
                 continue
             sign = torch.where(torch.randn(hd, generator=g) > 0, 1.0, -1.0)
-            view.keys[page, :, target % ps] = (6.0 * sign).to(dtype).cuda()
+            # a score of at most 100: far above the others, and its float32 rounding stays small
+            view.keys[page, :, target % ps] = (min(6.0, 100.0 / (0.4 * hd)) * sign).to(dtype).cuda()
             qkv[first + i, :nq * hd] = sign.repeat(nq).to(dtype)
             planted.append((r, p, target))
     assert len(planted) > 10
     qkv = qkv.cuda()
     gate = torch.randn((batch.num_tokens, nq * vd + 3), generator=g).to(dtype).cuda()
-    for use_gate in (False, True):
+    # every prompt kernel in turn: two query tiles per CTA, one, mma.sync fed by TMA, by cp.async
+    # (sizes that none of them takes run the kernel for any size whatever the switches say)
+    switches = [(True, 1, True, True), (False, 1, True, True), (False, 1, False, True),
+                (False, 1, False, False)]
+    saved = (ops.use_pp_prefill, ops.pp_prefill_min_ctas, ops.use_tc_prefill, ops.use_tma_prefill)
+    for k, use_gate in enumerate((False, True, False, True)):
         out = torch.empty((batch.num_tokens, nq * vd), dtype=dtype, device="cuda")
-        ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd, 0.4,
-                            None, out, storage=view.storage, value_dim=vd, chunk=chunk,
-                            gate=gate[:, :nq * vd] if use_gate else None)
+        ops.use_pp_prefill, ops.pp_prefill_min_ctas, ops.use_tc_prefill, ops.use_tma_prefill = switches[k]
+        try:
+            ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd, 0.4,
+                                None, out, storage=view.storage, value_dim=vd, chunk=chunk,
+                                gate=gate[:, :nq * vd] if use_gate else None)
+        finally:
+            ops.use_pp_prefill, ops.pp_prefill_min_ctas, ops.use_tc_prefill, ops.use_tma_prefill = saved
+        ops.check_errors()
         for j, r in enumerate(batch.host.requests):
             first, q, c = where[r]
             keys, values = gather_cache(view, table[j], c + q, ps)
@@ -263,7 +276,7 @@ def test_chunked_attention_with_planted_keys(ops, dtype, case):
             if use_gate:
                 want = want * torch.sigmoid(gate[first:first + q, :nq * vd].double().cpu())
             err = (out[first:first + q].double().cpu() - want).abs().max().item()
-            assert err < tol(dtype, 2e-5, 4e-2), (r, c, q, err)
+            assert err < tol(dtype, 4e-5, 4e-2), (r, c, q, err)
 
 
 # ------------------------------------------------------------------ the recurrence
@@ -273,7 +286,7 @@ def test_state_space_recurrence_over_steps(ops, dtype, geometry):
     heads, P, N, G = geometry
     g = torch.Generator().manual_seed(N)
     inner, wide = heads * P, heads * P + 2 * G * N
-    steps = Steps(ops, 3, state=StateNeeds({"m": ((heads, N, P), torch.float32)}), dtype=dtype)
+    steps = Steps(ops, 3, state=StateNeeds({"m": ((heads, P, N), torch.float32)}), dtype=dtype)
     L = 60
     xbc = {r: torch.randn((L, wide), generator=g).to(dtype) for r in "abc"}
     dt = {r: torch.randn((L, heads + 2), generator=g).to(dtype) for r in "abc"}
