@@ -39,7 +39,7 @@ __global__ void add_normed_rmsnorm_kernel(float* __restrict__ residual, const TD
                                           const void* __restrict__ weight_b, int wb_dtype, float eps_b,
                                           const void* __restrict__ weight, int w_dtype, float eps,
                                           TO* __restrict__ out, const int* __restrict__ rows, int H,
-                                          int write_back) {
+                                          int write_back, int vec4) {
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     pdl_launch_dependents();
@@ -48,6 +48,58 @@ __global__ void add_normed_rmsnorm_kernel(float* __restrict__ residual, const TD
     const int row = rows ? rows[b] : b;
     float* res = residual + static_cast<size_t>(row) * H;
     float ss = 0.f;
+    if (vec4) {
+        // four columns a thread: with a thread per four columns (the launcher's choice for the few
+        // rows of a decode step) every load of the row and of its partial sums is in flight at once
+        if (delta != nullptr) {
+            const TD* d0 = delta + static_cast<size_t>(row) * H;
+            for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+                F4 d = load4(d0 + i);
+#pragma unroll 4
+                for (int s = 1; s < splits; ++s) {
+                    const F4 e = load4(d0 + static_cast<size_t>(s) * split_stride + i);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) d.v[c] += e.v[c];
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) ss = fmaf(d.v[c], d.v[c], ss);
+                store4(row_buf + i, d);
+            }
+            ss = block_sum(ss, scratch);
+            const float rd = 1.0f / sqrtf(ss / static_cast<float>(H) + eps_b);
+            ss = 0.f;
+            for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+                const F4 d = load4(row_buf + i), wb = load4_any(weight_b, wb_dtype, i);
+                F4 r = load4(res + i);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    r.v[c] += d.v[c] * rd * wb.v[c];
+                    ss = fmaf(r.v[c], r.v[c], ss);
+                }
+                store4(row_buf + i, r);
+                if (write_back) store4(res + i, r);
+            }
+        } else {
+            for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+                const F4 r = load4(res + i);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) ss = fmaf(r.v[c], r.v[c], ss);
+                store4(row_buf + i, r);
+            }
+        }
+        if (out == nullptr) return;
+        ss = block_sum(ss, scratch);
+        const float rr = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
+        TO* o = out + static_cast<size_t>(b) * H;
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            const F4 w = load4_any(weight, w_dtype, i);
+            F4 r = load4(row_buf + i);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) r.v[c] = r.v[c] * rr * w.v[c];
+            store4(o + i, r);
+        }
+        return;
+    }
     if (delta != nullptr) {
         const TD* d0 = delta + static_cast<size_t>(row) * H;
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -164,7 +216,7 @@ __global__ void rotary_pairs_store_kernel(T* __restrict__ qkv, long long stride,
     const float pos = static_cast<float>(positions[t]);
     const int slot = slot_map != nullptr ? slot_map[t] : -1;
     const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-    for (int head = warp; head < nq + nkv; head += nwarps) {
+    for (int head = blockIdx.y * nwarps + warp; head < nq + nkv; head += nwarps * gridDim.y) {
         T* x = row + static_cast<size_t>(head) * hd;
         float v[8];
         float ss = 0.f;
@@ -199,7 +251,7 @@ __global__ void rotary_pairs_store_kernel(T* __restrict__ qkv, long long stride,
             }
         }
     }
-    if (slot >= 0) {
+    if (slot >= 0 && blockIdx.y == 0) {
         const T* vrow = row + static_cast<size_t>(nq + nkv) * hd;
         for (int g = 0; g < nkv; ++g) {
             T* dst = vcache + ((page * nkv + g) * page_size + off) * vd;
@@ -286,38 +338,49 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long x_stride, const T* __restri
     const float rate = expf(a_log[h]), bias = dt_bias[h], skip = Dskip[h];
     const int first = cu_q[r], last = cu_q[r + 1];
 
-    // one staged element: what thread `tid` fetches as its k-th of the block that starts at t0
-    auto fetch = [&](int t0, int k) -> float {
-        const int idx = tid + k * kScanThreads;
-        const int tok = idx / row_f, e = idx - tok * row_f;
-        const int t = t0 + tok;
-        if (tok >= kScanBlock || t >= last) return 0.f;
-        const T* row = xbc + static_cast<size_t>(t) * x_stride;
-        if (e < N) return to_float(row[inner + static_cast<size_t>(g) * N + e]);
-        if (e < 2 * N) return to_float(row[inner + static_cast<size_t>(groups + g) * N + (e - N)]);
-        if (e < 2 * N + kScanCols) {
-            const int p = cta_p0 + (e - 2 * N);
-            return p < P ? to_float(row[static_cast<size_t>(h) * P + p]) : 0.f;
-        }
-        const float dt = softplus_f(to_float(dt_raw[static_cast<size_t>(t) * dt_stride + h]) + bias);
-        return e == 2 * N + kScanCols ? dt : expf(-rate * dt);
-    };
-    float next[kLoads];
+    // A block's elements are fetched without branches (every thread's loads are in flight at
+    // once: a load behind a data-dependent branch would wait for the one before it) and kept as
+    // they were stored; they become float32, dt and decay when they are put into shared memory.
+    const int n_stage = kScanBlock * row_f;
+    T raw[kLoads];
+    auto issue = [&](int t0) {
 #pragma unroll
-    for (int k = 0; k < kLoads; ++k) next[k] = fetch(first, k);
-    int buf = 0;
-    for (int t0 = first; t0 < last; t0 += kScanBlock) {
-        float* cur = stage + buf * kScanBlock * row_f;
+        for (int k = 0; k < kLoads; ++k) {
+            const int idx = min(tid + k * kScanThreads, n_stage - 1);
+            const int tok = idx / row_f, e = idx - tok * row_f;
+            const int t = min(t0 + tok, last - 1);
+            const int p = min(cta_p0 + (e - 2 * N), P - 1);
+            const long long col = e < N ? inner + static_cast<long long>(g) * N + e
+                                  : (e < 2 * N ? inner + static_cast<long long>(groups + g) * N + (e - N)
+                                               : static_cast<long long>(h) * P + max(p, 0));
+            const T* src = e < 2 * N + kScanCols ? xbc + static_cast<size_t>(t) * x_stride + col
+                                                 : dt_raw + static_cast<size_t>(t) * dt_stride + h;
+            raw[k] = *src;
+        }
+    };
+    auto stash = [&](float* cur) {
 #pragma unroll
         for (int k = 0; k < kLoads; ++k) {
             const int idx = tid + k * kScanThreads;
-            if (idx < kScanBlock * row_f) cur[idx] = next[k];
+            if (idx >= n_stage) continue;
+            const int e = idx % row_f;
+            float v = to_float(raw[k]);
+            if (e >= 2 * N + kScanCols) {
+                const float dt = softplus_f(v + bias);
+                v = e == 2 * N + kScanCols ? dt : expf(-rate * dt);
+            } else if (e >= 2 * N && cta_p0 + (e - 2 * N) >= P) {
+                v = 0.f;
+            }
+            cur[idx] = v;
         }
+    };
+    if (first < last) issue(first);
+    int buf = 0;
+    for (int t0 = first; t0 < last; t0 += kScanBlock) {
+        float* cur = stage + buf * n_stage;
+        stash(cur);
         __syncthreads();
-        if (t0 + kScanBlock < last) {
-#pragma unroll
-            for (int k = 0; k < kLoads; ++k) next[k] = fetch(t0 + kScanBlock, k);
-        }
+        if (t0 + kScanBlock < last) issue(t0 + kScanBlock);
         const int n_tok = min(kScanBlock, last - t0);
         if (p0 < P) {
             for (int tok = 0; tok < n_tok; ++tok) {
@@ -418,7 +481,12 @@ SOMI_API int somi_add_normed_rmsnorm(float* residual, const void* delta, int del
     if (splits > 1 && delta_dtype != SOMI_F32) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = sizeof(float) * H;
     if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
-    const int threads = block_for(H / 2);
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const int vec4 = (H & 3) == 0 && aligned(residual) && aligned(delta) && aligned(weight_b) &&
+                     aligned(weight) && aligned(out) && (split_stride & 3) == 0;
+    // few rows (a decode step): a thread per four columns; many rows: a quarter of that
+    const int threads = vec4 ? min(1024, max(32, (((n_out <= 512 ? H / 4 : H / 16) + 31) / 32) * 32))
+                             : block_for(H / 2);
 #define SOMI_LAUNCH_SN(TD, TO)                                                                    \
     do {                                                                                          \
         if (smem > 48 * 1024)                                                                     \
@@ -427,7 +495,7 @@ SOMI_API int somi_add_normed_rmsnorm(float* residual, const void* delta, int del
         launch_pdl(add_normed_rmsnorm_kernel<TD, TO>, dim3(n_out), dim3(threads), smem, stream,   \
                    residual, static_cast<const TD*>(delta), splits, split_stride, weight_b,       \
                    wb_dtype, eps_b, weight, w_dtype, eps, static_cast<TO*>(out), rows, H,         \
-                   write_back);                                                                   \
+                   write_back, vec4);                                                             \
     } while (0)
     if (delta_dtype == SOMI_F32 && out_dtype == SOMI_F32) SOMI_LAUNCH_SN(float, float);
     else if (delta_dtype == SOMI_F32) SOMI_LAUNCH_SN(float, __nv_bfloat16);
@@ -452,7 +520,7 @@ SOMI_API int somi_causal_conv(const void* u, int dtype, long long in_stride, con
     const int chunks = max(1, min(64, (C + tb - 1) / tb));
 #define SOMI_LAUNCH_CONV(TT)                                                                     \
     do {                                                                                         \
-        launch_pdl(causal_conv_kernel<TT>, dim3((T + 3) / 4, max(1, min(8, C / 256))),           \
+        launch_pdl(causal_conv_kernel<TT>, dim3((T + 3) / 4, max(1, min(T <= 64 ? 128 : 8, (C + 63) / 64))), \
                    dim3(64, 4), 0, stream, static_cast<const TT*>(u), in_stride, w, bias,        \
                    static_cast<const TT*>(state), cu_q, token_request, state_slot,               \
                    static_cast<TT*>(out), out_stride, C, taps, act, add_input, T);               \
@@ -475,13 +543,15 @@ SOMI_API int somi_rotary_pairs_store(void* qkv, int dtype, long long stride, con
     if (hd <= 0 || hd > 256 || vd <= 0 || rot < 0 || rot > hd || (rot & 1) || nq <= 0 || nkv <= 0)
         return SOMI_ERR_UNSUPPORTED;
     const int threads = 32 * min(8, nq + nkv);
+    // few tokens: a warp per head, so that a step of single tokens still fills the SMs
+    const dim3 grid(T, T <= 256 ? (nq + nkv + 7) / 8 : 1);
     if (dtype == SOMI_F32)
-        launch_pdl(rotary_pairs_store_kernel<float>, dim3(T), dim3(threads), 0, stream,
+        launch_pdl(rotary_pairs_store_kernel<float>, grid, dim3(threads), 0, stream,
                    static_cast<float*>(qkv), stride, positions, inv_freq, nq, nkv, hd, vd, rot,
                    unit_norm, eps, slot_map, static_cast<float*>(kcache),
                    static_cast<float*>(vcache), page_size);
     else
-        launch_pdl(rotary_pairs_store_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+        launch_pdl(rotary_pairs_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream,
                    static_cast<__nv_bfloat16*>(qkv), stride, positions, inv_freq, nq, nkv, hd, vd,
                    rot, unit_norm, eps, slot_map, static_cast<__nv_bfloat16*>(kcache),
                    static_cast<__nv_bfloat16*>(vcache), page_size);
