@@ -296,7 +296,8 @@ __global__ void softcap_kernel(float* __restrict__ x, float cap, long long n) {
 // of this step; a warp owns kScanColsPerWarp columns, a lane the state rows n = lane + 32 j.
 // Rows are staged kScanBlock at a time in shared memory (B, C, the CTA's x columns, dt and the
 // decay, each computed once), the next block's loads in flight while this one is worked on.
-// The sum over n is a fixed tree (j, then lanes), so y does not depend on how the rows were cut.
+// The sum over n is taken in a fixed order (j, then lanes), so y does not depend on how the rows were cut.
+// Index arithmetic of the staging is done once per thread, not per element.
 constexpr int kScanWarps = 4;
 constexpr int kScanColsPerWarp = 4;
 constexpr int kScanCols = kScanWarps * kScanColsPerWarp;
@@ -316,7 +317,8 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long x_stride, const T* __restri
                 const int* __restrict__ state_slot, float* __restrict__ y, int heads, int groups,
                 int N, int P) {
     extern __shared__ float stage[];                       // [2][kScanBlock][row_f]
-    constexpr int kLoads = (kScanBlock * (64 * NPL + kScanCols + 2) + kScanThreads - 1) / kScanThreads;
+    // column slots of a staged row that one thread fetches: e = tid + c * kScanThreads < 2 N + kScanCols
+    constexpr int kSlots = (64 * NPL + kScanCols + kScanThreads - 1) / kScanThreads;
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x, h = blockIdx.y;
@@ -326,6 +328,7 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long x_stride, const T* __restri
     const int g = h / (heads / groups);
     const int inner = heads * P;
     const int row_f = 2 * N + kScanCols + 2;               // B, C, x columns, dt, decay
+    const int n_stage = kScanBlock * row_f;
     float* st = state + (static_cast<size_t>(state_slot[r]) * heads + h) * N * P;
     float m[NPL][kScanColsPerWarp];
 #pragma unroll
@@ -338,42 +341,56 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long x_stride, const T* __restri
     const float rate = expf(a_log[h]), bias = dt_bias[h], skip = Dskip[h];
     const int first = cu_q[r], last = cu_q[r + 1];
 
-    // A block's elements are fetched without branches (every thread's loads are in flight at
-    // once: a load behind a data-dependent branch would wait for the one before it) and kept as
-    // they were stored; they become float32, dt and decay when they are put into shared memory.
-    const int n_stage = kScanBlock * row_f;
-    T raw[kLoads];
+    // where this thread's column slots lie in a row of xbc (-1: nothing to fetch, zero is staged)
+    int col_off[kSlots];
+#pragma unroll
+    for (int c = 0; c < kSlots; ++c) {
+        const int e = tid + c * kScanThreads;
+        int off = -1;
+        if (e < N) off = inner + g * N + e;
+        else if (e < 2 * N) off = inner + (groups + g) * N + (e - N);
+        else if (e < 2 * N + kScanCols && cta_p0 + (e - 2 * N) < P) off = h * P + cta_p0 + (e - 2 * N);
+        col_off[c] = off;
+    }
+    T raw[kSlots][kScanBlock];
+    T raw_dt = from_float<T>(0.f);
+    // the loads of a block are all in flight at once; they become float32 (and dt, decay) when
+    // they are put into shared memory, one block later
     auto issue = [&](int t0) {
 #pragma unroll
-        for (int k = 0; k < kLoads; ++k) {
-            const int idx = min(tid + k * kScanThreads, n_stage - 1);
-            const int tok = idx / row_f, e = idx - tok * row_f;
-            const int t = min(t0 + tok, last - 1);
-            const int p = min(cta_p0 + (e - 2 * N), P - 1);
-            const long long col = e < N ? inner + static_cast<long long>(g) * N + e
-                                  : (e < 2 * N ? inner + static_cast<long long>(groups + g) * N + (e - N)
-                                               : static_cast<long long>(h) * P + max(p, 0));
-            const T* src = e < 2 * N + kScanCols ? xbc + static_cast<size_t>(t) * x_stride + col
-                                                 : dt_raw + static_cast<size_t>(t) * dt_stride + h;
-            raw[k] = *src;
+        for (int tok = 0; tok < kScanBlock; ++tok) {
+            if (t0 + tok < last) {
+                const T* row = xbc + static_cast<size_t>(t0 + tok) * x_stride;
+#pragma unroll
+                for (int c = 0; c < kSlots; ++c)
+                    if (col_off[c] >= 0) raw[c][tok] = row[col_off[c]];
+            }
         }
+        if (tid < kScanBlock && t0 + tid < last)
+            raw_dt = dt_raw[static_cast<size_t>(t0 + tid) * dt_stride + h];
     };
     auto stash = [&](float* cur) {
 #pragma unroll
-        for (int k = 0; k < kLoads; ++k) {
-            const int idx = tid + k * kScanThreads;
-            if (idx >= n_stage) continue;
-            const int e = idx % row_f;
-            float v = to_float(raw[k]);
-            if (e >= 2 * N + kScanCols) {
-                const float dt = softplus_f(v + bias);
-                v = e == 2 * N + kScanCols ? dt : expf(-rate * dt);
-            } else if (e >= 2 * N && cta_p0 + (e - 2 * N) >= P) {
-                v = 0.f;
+        for (int c = 0; c < kSlots; ++c) {
+            const int e = tid + c * kScanThreads;
+            if (e < 2 * N + kScanCols) {
+#pragma unroll
+                for (int tok = 0; tok < kScanBlock; ++tok)
+                    cur[tok * row_f + e] = col_off[c] >= 0 ? to_float(raw[c][tok]) : 0.f;
             }
-            cur[idx] = v;
+        }
+        if (tid < kScanBlock) {
+            const float dt = softplus_f(to_float(raw_dt) + bias);
+            cur[tid * row_f + 2 * N + kScanCols] = dt;
+            cur[tid * row_f + 2 * N + kScanCols + 1] = expf(-rate * dt);
         }
     };
+    // A lane's partial sums over its own state rows go to shared memory, [row of the block][column]
+    // [lane] with rows of 33 floats; after the block's rows, lane 4 t + c adds up the 32 partial
+    // sums of (row t, column c) in lane order.  The loop over rows then carries nothing but the
+    // state itself, one multiply-add deep, so consecutive rows overlap.
+    static_assert(kScanBlock * kScanColsPerWarp == 32, "one (row, column) pair per lane");
+    float* part = stage + 2 * n_stage + warp * (32 * 33);
     if (first < last) issue(first);
     int buf = 0;
     for (int t0 = first; t0 < last; t0 += kScanBlock) {
@@ -404,13 +421,20 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long x_stride, const T* __restri
                     }
                 }
 #pragma unroll
-                for (int i = 0; i < kScanColsPerWarp; ++i) {
-                    const float s = warp_sum(acc[i]);
-                    if (lane == 0 && p0 + i < P)
-                        y[static_cast<size_t>(t0 + tok) * inner + static_cast<size_t>(h) * P + p0 + i] =
-                            fmaf(skip, xv[i], s);
-                }
+                for (int i = 0; i < kScanColsPerWarp; ++i)
+                    part[(tok * kScanColsPerWarp + i) * 33 + lane] = acc[i];
             }
+            __syncwarp();
+            const int tok = lane / kScanColsPerWarp, col = lane % kScanColsPerWarp;
+            if (tok < n_tok && p0 + col < P) {
+                const float* mine = part + lane * 33;
+                float v = 0.f;
+#pragma unroll
+                for (int k = 0; k < 32; ++k) v += mine[k];
+                y[static_cast<size_t>(t0 + tok) * inner + static_cast<size_t>(h) * P + p0 + col] =
+                    fmaf(skip, cur[tok * row_f + 2 * N + warp * kScanColsPerWarp + col], v);
+            }
+            __syncwarp();
         }
         buf ^= 1;       // the block after the next overwrites this buffer only behind the next barrier
     }
@@ -580,7 +604,7 @@ SOMI_API int somi_softcap(float* x, float cap, long long n, cudaStream_t stream)
     return launch_status();
 }
 
-SOMI_API int somi_ssm_scan_max_state() { return 256; }
+SOMI_API int somi_ssm_scan_max_state() { return 512; }
 
 SOMI_API int somi_ssm_scan(const void* xbc, int dtype, long long x_stride, const void* dt_raw,
                            long long dt_stride, const float* dt_bias, const float* a_log,
@@ -588,21 +612,28 @@ SOMI_API int somi_ssm_scan(const void* xbc, int dtype, long long x_stride, const
                            float* y, int R, int heads, int groups, int N, int P,
                            cudaStream_t stream) {
     if (R <= 0) return 0;
-    if (N <= 0 || N > 256 || P <= 0 || heads <= 0 || groups <= 0 || heads % groups)
+    if (N <= 0 || N > 512 || P <= 0 || heads <= 0 || groups <= 0 || heads % groups)
         return SOMI_ERR_UNSUPPORTED;
     dim3 grid(R, heads, (P + kScanCols - 1) / kScanCols);
     const int npl = (N + 31) / 32;
-    const size_t smem = sizeof(float) * 2 * kScanBlock * (2 * N + kScanCols + 2);
+    const size_t smem = sizeof(float) * (2 * kScanBlock * (2 * N + kScanCols + 2) + kScanWarps * 32 * 33);
 #define SOMI_LAUNCH_SCAN(TT, NPL)                                                                \
-    launch_pdl(ssm_scan_kernel<TT, NPL>, grid, dim3(kScanThreads), smem, stream,                 \
-               static_cast<const TT*>(xbc), x_stride, static_cast<const TT*>(dt_raw), dt_stride, \
-               dt_bias, a_log, Dskip, state, cu_q, state_slot, y, heads, groups, N, P)
+    do {                                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            cudaFuncSetAttribute(ssm_scan_kernel<TT, NPL>,                                       \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        launch_pdl(ssm_scan_kernel<TT, NPL>, grid, dim3(kScanThreads), smem, stream,             \
+                   static_cast<const TT*>(xbc), x_stride, static_cast<const TT*>(dt_raw),        \
+                   dt_stride, dt_bias, a_log, Dskip, state, cu_q, state_slot, y, heads, groups,  \
+                   N, P);                                                                        \
+    } while (0)
 #define SOMI_SCAN_BY_N(TT)                                                                       \
     do {                                                                                         \
         if (npl <= 1) SOMI_LAUNCH_SCAN(TT, 1);                                                   \
         else if (npl <= 2) SOMI_LAUNCH_SCAN(TT, 2);                                              \
         else if (npl <= 4) SOMI_LAUNCH_SCAN(TT, 4);                                              \
-        else SOMI_LAUNCH_SCAN(TT, 8);                                                            \
+        else if (npl <= 8) SOMI_LAUNCH_SCAN(TT, 8);                                              \
+        else SOMI_LAUNCH_SCAN(TT, 16);                                                           \
     } while (0)
     if (dtype == SOMI_F32) SOMI_SCAN_BY_N(float);
     else SOMI_SCAN_BY_N(__nv_bfloat16);

@@ -214,7 +214,7 @@ def gather_cache(view, table_row, length, page_size):
     (4, 2, 12, 20, 9, 8), (2, 1, 16, 16, 21, 4), (3, 3, 5, 3, 1, 4), (2, 2, 32, 8, 64, 16),
     (1, 1, 40, 40, 300, 16),
     # head sizes of the tensor-core kernels (bfloat16): the same mask as one signed number
-    (4, 2, 64, 64, 96, 16), (8, 1, 128, 128, 300, 16), (4, 4, 128, 128, 50, 8)])
+    (4, 2, 64, 64, 96, 16), (8, 1, 128, 128, 300, 16), (4, 4, 128, 128, 50, 8), (2, 2, 64, 64, 5, 16)])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_chunked_attention_with_planted_keys(ops, dtype, case):
     """Prompt portions and single tokens whose queries point at one scaled key each: the chunk's
@@ -280,7 +280,8 @@ def test_chunked_attention_with_planted_keys(ops, dtype, case):
 
 
 # ------------------------------------------------------------------ the recurrence
-@pytest.mark.parametrize("geometry", [(3, 10, 12, 1), (4, 6, 40, 2), (1, 5, 70, 1), (8, 16, 128, 4), (2, 7, 3, 2)])
+@pytest.mark.parametrize("geometry", [(3, 10, 12, 1), (4, 6, 40, 2), (1, 5, 70, 1), (8, 16, 128, 4), (2, 7, 3, 2),
+                                      (2, 20, 300, 1)])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_state_space_recurrence_over_steps(ops, dtype, geometry):
     heads, P, N, G = geometry
@@ -345,6 +346,8 @@ def test_table_routed_experts(ops, dtype, shape, tokens):
     steps = Steps(ops, 1, dtype=dtype, max_len=256)
     batch, _ = steps.step({"a": tokens})
     ids = torch.randint(0, vocab, (tokens,), generator=g)
+    if tokens == 200:
+        ids[:150] = 7          # most experts get no token at all, some a full tile and more
     batch.token_ids.copy_(ids.to(torch.int32))
     x = torch.randn((tokens, H), generator=g).to(dtype)
     got = part.forward(x.cuda(), batch)
