@@ -93,6 +93,29 @@ __global__ void clamped_gate_up_kernel(const T* __restrict__ gu, T* __restrict__
                                        long long n, float limit, float alpha) {
     pdl_launch_dependents();
     pdl_wait();
+    if (sizeof(T) == 2 && (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        // four outputs a thread: eight inputs in one 16-byte load
+        const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(gu);
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+        for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n;
+             i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(in + 2 * i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float y[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float g = fminf(__low2float(h[e]), limit);
+                const float u = fminf(fmaxf(__high2float(h[e]), -limit), limit);
+                y[e] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+            }
+            const __nv_bfloat162 y01 = __floats2bfloat162_rn(y[0], y[1]), y23 = __floats2bfloat162_rn(y[2], y[3]);
+            uint2 packed;
+            packed.x = *reinterpret_cast<const uint32_t*>(&y01);
+            packed.y = *reinterpret_cast<const uint32_t*>(&y23);
+            *reinterpret_cast<uint2*>(o + i) = packed;
+        }
+        return;
+    }
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const float g = fminf(to_float(gu[2 * i]), limit);

@@ -145,7 +145,7 @@ __global__ void causal_conv_kernel(const T* __restrict__ u, long long in_stride,
                                    const int* __restrict__ token_request,
                                    const int* __restrict__ state_slot, T* __restrict__ out,
                                    long long out_stride, int C, int taps, int act, int add_input,
-                                   int n_tokens) {
+                                   int n_tokens, int vec4) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x * blockDim.y + threadIdx.y;
@@ -153,6 +153,32 @@ __global__ void causal_conv_kernel(const T* __restrict__ u, long long in_stride,
     const int req = token_request[t];
     const int local = t - cu_q[req];
     const T* st = state + static_cast<size_t>(state_slot[req]) * (taps - 1) * C;
+    if (vec4) {
+        for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < C; c += gridDim.y * blockDim.x * 4) {
+            const F4 own = load4(u + static_cast<size_t>(t) * in_stride + c);
+            F4 acc = F4{{0.f, 0.f, 0.f, 0.f}};
+            for (int d = taps - 1; d >= 0; --d) {      // oldest input first
+                const F4 v = d == 0 ? own
+                             : (local - d >= 0 ? load4(u + static_cast<size_t>(t - d) * in_stride + c)
+                                               : load4(st + static_cast<size_t>(taps - 1 + local - d) * C + c));
+                const F4 ww = load4(w + static_cast<size_t>(taps - 1 - d) * C + c);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc.v[e] = fmaf(ww.v[e], v.v[e], acc.v[e]);
+            }
+            if (bias != nullptr) {
+                const F4 bb = load4(bias + c);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc.v[e] += bb.v[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (act == 1) acc.v[e] = acc.v[e] / (1.0f + expf(-acc.v[e]));
+                if (add_input) acc.v[e] += own.v[e];
+            }
+            store4(out + static_cast<size_t>(t) * out_stride + c, acc);
+        }
+        return;
+    }
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         const float own = to_float(u[static_cast<size_t>(t) * in_stride + c]);
         float acc = 0.f;
@@ -218,36 +244,42 @@ __global__ void rotary_pairs_store_kernel(T* __restrict__ qkv, long long stride,
     const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
     for (int head = blockIdx.y * nwarps + warp; head < nq + nkv; head += nwarps * gridDim.y) {
         T* x = row + static_cast<size_t>(head) * hd;
-        float v[8];
+        // a lane owns the pairs (2 i, 2 i + 1), i = lane + 32 j: one sine and cosine per pair; an
+        // odd width's last element is a pair whose second half does not exist
+        float va[4], vb[4];
         float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int e = lane + 32 * j;
-            v[j] = 0.f;
+        for (int j = 0; j < 4; ++j) {
+            const int e = 2 * (lane + 32 * j);
+            va[j] = vb[j] = 0.f;
             if (e < hd) {
                 float a = to_float(x[e]);
-                if (e < rot) {
-                    float s, c;
-                    sincosf(pos * inv_freq[e >> 1], &s, &c);
-                    const float other = to_float(x[e ^ 1]);
-                    a = (e & 1) ? fmaf(a, c, other * s) : fmaf(a, c, -(other * s));
+                float b = e + 1 < hd ? to_float(x[e + 1]) : 0.f;
+                if (e + 1 < rot) {
+                    float sn, cs;
+                    sincosf(pos * inv_freq[e >> 1], &sn, &cs);
+                    const float ra = fmaf(a, cs, -(b * sn)), rb = fmaf(b, cs, a * sn);
+                    a = ra;
+                    b = rb;
                 }
-                v[j] = a;
-                ss = fmaf(a, a, ss);
+                va[j] = a;
+                vb[j] = b;
+                ss = fmaf(a, a, fmaf(b, b, ss));
             }
         }
         ss = warp_sum(ss);         // also orders the reads of x before the writes below
         const float r = unit_norm ? 1.0f / sqrtf(ss / static_cast<float>(hd) + eps) : 1.0f;
         T* dst = nullptr;
-        if (head >= nq && slot >= 0)
-            dst = kcache + ((page * nkv + (head - nq)) * page_size + off) * hd;
+        if (head < nq) dst = x;
+        else if (slot >= 0) dst = kcache + ((page * nkv + (head - nq)) * page_size + off) * hd;
+        if (dst != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int e = lane + 32 * j;
-            if (e < hd) {
-                const T o = from_float<T>(v[j] * r);
-                if (head < nq) x[e] = o;
-                else if (dst != nullptr) dst[e] = o;
+            for (int j = 0; j < 4; ++j) {
+                const int e = 2 * (lane + 32 * j);
+                if (e < hd) {
+                    dst[e] = from_float<T>(va[j] * r);
+                    if (e + 1 < hd) dst[e + 1] = from_float<T>(vb[j] * r);
+                }
             }
         }
     }
@@ -542,12 +574,21 @@ SOMI_API int somi_causal_conv(const void* u, int dtype, long long in_stride, con
     if (taps < 1 || taps > kConvMaxTaps || R <= 0 || C <= 0) return SOMI_ERR_UNSUPPORTED;
     const int tb = min(256, ((C + 31) / 32) * 32);
     const int chunks = max(1, min(64, (C + tb - 1) / tb));
+    // four channels a thread where every row starts on a vector boundary (16 bytes of float32, 8 of
+    // bfloat16)
+    const uintptr_t mask = dtype == SOMI_F32 ? 15 : 7;
+    const int vec4 = (C & 3) == 0 && (in_stride & 3) == 0 && (out_stride & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(out) |
+                       reinterpret_cast<uintptr_t>(state)) & mask) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
+    const int per = vec4 ? 4 : 1;
 #define SOMI_LAUNCH_CONV(TT)                                                                     \
     do {                                                                                         \
-        launch_pdl(causal_conv_kernel<TT>, dim3((T + 3) / 4, max(1, min(T <= 64 ? 128 : 8, (C + 63) / 64))), \
+        launch_pdl(causal_conv_kernel<TT>,                                                       \
+                   dim3((T + 3) / 4, max(1, min(T <= 64 ? 128 : 8, (C / per + 63) / 64))),       \
                    dim3(64, 4), 0, stream, static_cast<const TT*>(u), in_stride, w, bias,        \
                    static_cast<const TT*>(state), cu_q, token_request, state_slot,               \
-                   static_cast<TT*>(out), out_stride, C, taps, act, add_input, T);               \
+                   static_cast<TT*>(out), out_stride, C, taps, act, add_input, T, vec4);         \
         if (taps > 1)                                                                            \
             launch_pdl(causal_conv_state_kernel<TT>, dim3(R, chunks), dim3(tb), 0, stream,       \
                        static_cast<const TT*>(u), in_stride, static_cast<TT*>(state), cu_q,      \
