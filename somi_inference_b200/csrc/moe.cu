@@ -7,11 +7,16 @@
 //             entry's result does not depend on the tile it fell into or on the rest of the step.
 //             Epilogues: the experts' gated activation over row-interleaved gate/up weights, or
 //             float32 rows scattered back to the entries' places.
-//   combine:  out[t] = weight * sum_k y[t * top + k] (+ the shared expert's rows), float32.
+//   matrix-vector: a step of few entries needs no grouping: every entry streams the rows of its
+//             own expert (bfloat16, 16-byte loads, two rows a warp), with the same two epilogues.
+//   gather / activation: what stands around the library's grouped product in prompt-sized
+//             bfloat16 steps: the rows in the grouped order, and the experts' gated activation.
+//   combine:  out[t] = weight * sum_k y[row of entry t * top + k] (+ the shared expert's rows), float32.
 //
 // A product over all rows with one weight matrix (a shared expert) is the same kernel with one
 // group.  Everything is decided on the device: the launches depend on the step's layout only.
 #include "common.cuh"
+#include "vec4.cuh"
 
 namespace somi {
 
@@ -292,6 +297,30 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
                                    long long n, float* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
+    if ((H & 3) == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(extra) |
+                          reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n;
+             i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+            const long long t = i / H;
+            const int c = static_cast<int>(i - t * H);
+            F4 s = F4{{0.f, 0.f, 0.f, 0.f}};
+            for (int k = 0; k < top; ++k) {
+                const long long e = t * top + k;
+                const F4 v = load4(y + (place != nullptr ? place[e] : e) * H + c);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) s.v[q] += v.v[q];
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) s.v[q] *= weight;
+            if (extra != nullptr) {
+                const F4 x = load4(extra + i);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) s.v[q] += x.v[q];
+            }
+            store4(out + i, s);
+        }
+        return;
+    }
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long t = i / H;

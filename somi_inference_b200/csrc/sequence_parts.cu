@@ -296,9 +296,22 @@ __global__ void rotary_pairs_store_kernel(T* __restrict__ qkv, long long stride,
 // x[t, c] *= sigmoid(g[t, c]); g's rows lie `g_stride` elements apart.
 template <typename T>
 __global__ void sigmoid_gate_mul_kernel(T* __restrict__ x, const T* __restrict__ g, long long g_stride,
-                                        int C, long long n) {
+                                        int C, long long n, int vec4) {
     pdl_launch_dependents();
     pdl_wait();
+    if (vec4) {
+        for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n;
+             i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+            const long long t = i / C;
+            const int c = static_cast<int>(i - t * C);
+            const F4 z = load4(g + t * g_stride + c);
+            F4 v = load4(x + i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v.v[e] = v.v[e] / (1.0f + expf(-z.v[e]));
+            store4(x + i, v);
+        }
+        return;
+    }
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long t = i / C;
@@ -486,7 +499,8 @@ template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z,
                                            long long z_stride, const void* __restrict__ weight,
                                            int w_dtype, float eps, T* __restrict__ out, int C,
-                                           int groups) {
+                                           int groups, int vec4) {
+    extern __shared__ __align__(16) float vals[];          // the part's gated values
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -494,20 +508,40 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     const int n = C / groups, c0 = part * n;
     const float* yr = y + static_cast<size_t>(t) * C + c0;
     const T* zr = z + static_cast<size_t>(t) * z_stride + c0;
+    T* o = out + static_cast<size_t>(t) * C + c0;
     float ss = 0.f;
+    if (vec4) {
+        for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+            const F4 zz = load4(zr + i);
+            F4 v = load4(yr + i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                v.v[e] *= zz.v[e] / (1.0f + expf(-zz.v[e]));
+                ss = fmaf(v.v[e], v.v[e], ss);
+            }
+            store4(vals + i, v);
+        }
+        ss = block_sum(ss, scratch);
+        const float r = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
+        for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+            const F4 w = load4_any(weight, w_dtype, c0 + i);
+            F4 v = load4(vals + i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v.v[e] = v.v[e] * r * w.v[e];
+            store4(o + i, v);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float zz = to_float(zr[i]);
         const float v = yr[i] * (zz / (1.0f + expf(-zz)));
+        vals[i] = v;
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
     const float r = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
-    T* o = out + static_cast<size_t>(t) * C + c0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float zz = to_float(zr[i]);
-        const float v = yr[i] * (zz / (1.0f + expf(-zz)));
-        o[i] = from_float<T>(v * r * load_as_float(weight, w_dtype, c0 + i));
-    }
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        o[i] = from_float<T>(vals[i] * r * load_as_float(weight, w_dtype, c0 + i));
 }
 
 }  // namespace somi
@@ -627,13 +661,18 @@ SOMI_API int somi_sigmoid_gate_mul(void* x, const void* g, int dtype, long long 
                                    int C, cudaStream_t stream) {
     const long long n = T * C;
     if (n <= 0) return 0;
-    const int blocks = static_cast<int>(((n + 255) / 256) < 148LL * 16 ? ((n + 255) / 256) : 148LL * 16);
+    const uintptr_t mask = dtype == SOMI_F32 ? 15 : 7;
+    const int vec4 = (C & 3) == 0 && (g_stride & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g)) & mask) == 0;
+    const long long work = vec4 ? n / 4 : n;
+    const int blocks = static_cast<int>(((work + 255) / 256) < 148LL * 16 ? ((work + 255) / 256) : 148LL * 16);
     if (dtype == SOMI_F32)
         launch_pdl(sigmoid_gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream,
-                   static_cast<float*>(x), static_cast<const float*>(g), g_stride, C, n);
+                   static_cast<float*>(x), static_cast<const float*>(g), g_stride, C, n, vec4);
     else
         launch_pdl(sigmoid_gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
-                   static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g), g_stride, C, n);
+                   static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g), g_stride, C, n,
+                   vec4);
     return launch_status();
 }
 
@@ -688,14 +727,25 @@ SOMI_API int somi_gated_group_rmsnorm(const float* y, const void* z, int dtype, 
                                       int C, int groups, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (groups <= 0 || C % groups) return SOMI_ERR_UNSUPPORTED;
-    const int threads = block_for(C / groups / 2);
-    if (dtype == SOMI_F32)
-        launch_pdl(gated_group_rmsnorm_kernel<float>, dim3(T, groups), dim3(threads), 0, stream, y,
-                   static_cast<const float*>(z), z_stride, weight, w_dtype, eps,
-                   static_cast<float*>(out), C, groups);
-    else
-        launch_pdl(gated_group_rmsnorm_kernel<__nv_bfloat16>, dim3(T, groups), dim3(threads), 0,
-                   stream, y, static_cast<const __nv_bfloat16*>(z), z_stride, weight, w_dtype, eps,
-                   static_cast<__nv_bfloat16*>(out), C, groups);
+    const int n = C / groups;
+    const size_t smem = sizeof(float) * n;
+    if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
+    const uintptr_t mask = dtype == SOMI_F32 ? 15 : 7;
+    const int vec4 = (n & 3) == 0 && (z_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(out)) & mask) == 0;
+    const int threads = block_for(vec4 ? n / 4 : n / 2);
+#define SOMI_LAUNCH_GGN(TT)                                                                       \
+    do {                                                                                          \
+        if (smem > 48 * 1024)                                                                     \
+            cudaFuncSetAttribute(gated_group_rmsnorm_kernel<TT>,                                  \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+        launch_pdl(gated_group_rmsnorm_kernel<TT>, dim3(T, groups), dim3(threads), smem, stream, y, \
+                   static_cast<const TT*>(z), z_stride, weight, w_dtype, eps,                     \
+                   static_cast<TT*>(out), C, groups, vec4);                                       \
+    } while (0)
+    if (dtype == SOMI_F32) SOMI_LAUNCH_GGN(float);
+    else SOMI_LAUNCH_GGN(__nv_bfloat16);
+#undef SOMI_LAUNCH_GGN
     return launch_status();
 }
