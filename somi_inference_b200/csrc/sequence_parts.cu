@@ -230,7 +230,7 @@ __global__ void causal_conv_state_kernel(const T* __restrict__ u, long long in_s
 template <typename T>
 __global__ void rotary_pairs_store_kernel(T* __restrict__ qkv, long long stride,
                                           const int* __restrict__ positions,
-                                          const float* __restrict__ inv_freq, int nq, int nkv, int hd,
+                                          const double* __restrict__ inv_freq, int nq, int nkv, int hd,
                                           int vd, int rot, int unit_norm, float eps,
                                           const int* __restrict__ slot_map, T* __restrict__ kcache,
                                           T* __restrict__ vcache, int page_size) {
@@ -239,7 +239,11 @@ __global__ void rotary_pairs_store_kernel(T* __restrict__ qkv, long long stride,
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     T* row = qkv + static_cast<size_t>(t) * stride;
-    const float pos = static_cast<float>(positions[t]);
+    // The angle position * frequency is formed in float64 and brought into [-pi, pi] there: in
+    // float32 its rounding grows with the position (half an ulp of an angle of a thousand radians
+    // is 3e-5, which a peaked softmax turns into an error of that relative size); sine and cosine
+    // of the reduced angle are float32.
+    const double pos = static_cast<double>(positions[t]);
     const int slot = slot_map != nullptr ? slot_map[t] : -1;
     const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
     for (int head = blockIdx.y * nwarps + warp; head < nq + nkv; head += nwarps * gridDim.y) {
@@ -257,7 +261,9 @@ __global__ void rotary_pairs_store_kernel(T* __restrict__ qkv, long long stride,
                 float b = e + 1 < hd ? to_float(x[e + 1]) : 0.f;
                 if (e + 1 < rot) {
                     float sn, cs;
-                    sincosf(pos * inv_freq[e >> 1], &sn, &cs);
+                    double angle = pos * inv_freq[e >> 1];
+                    angle -= 6.283185307179586476925286766559 * rint(angle * 0.15915494309189533576888376337251);
+                    sincosf(static_cast<float>(angle), &sn, &cs);
                     const float ra = fmaf(a, cs, -(b * sn)), rb = fmaf(b, cs, a * sn);
                     a = ra;
                     b = rb;
@@ -635,7 +641,7 @@ SOMI_API int somi_causal_conv(const void* u, int dtype, long long in_stride, con
 }
 
 SOMI_API int somi_rotary_pairs_store(void* qkv, int dtype, long long stride, const int* positions,
-                                     const float* inv_freq, int T, int nq, int nkv, int hd, int vd,
+                                     const double* inv_freq, int T, int nq, int nkv, int hd, int vd,
                                      int rot, int unit_norm, float eps, const int* slot_map,
                                      void* kcache, void* vcache, int page_size, cudaStream_t stream) {
     if (T <= 0) return 0;

@@ -748,13 +748,14 @@ class CudaOps:
                            eps, slot_map, kcache, vcache) -> None:
         """Rows of `qkv` hold nq query heads and nkv key heads of `hd` elements, then nkv value
         heads of `vd`.  Neighbouring pairs (2i, 2i+1) below `rotary_dim` of every query and key
-        head turn by position * inv_freq[i]; with `unit_norm` each head is then divided by its
+        head turn by position * inv_freq[i] (`inv_freq` float64: the angle is reduced in float64, its
+        sine and cosine are float32); with `unit_norm` each head is then divided by its
         root mean square (eps inside the root).  Queries are rewritten in place; keys and values
         go to their cache slots (`slot_map` None: nothing is stored)."""
         _check(positions, inv_freq, slot_map, kcache, vcache)
         if not (qkv.is_cuda and qkv.stride(1) == 1 and qkv.shape[1] >= (nq + nkv) * hd + nkv * vd):
             raise KernelError("rotary_pairs_store takes a device tensor with contiguous rows")
-        assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(1, rotary_dim // 2)
+        assert inv_freq.dtype == torch.float64 and inv_freq.numel() >= max(1, rotary_dim // 2)
         page_size = 1
         if slot_map is not None:
             assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype

@@ -13,7 +13,8 @@ Key and value widths may differ; query head i reads key/value head i // (heads /
 One product makes q, k, v and the gate's logits; the convolution reads the first three out of
 it and keeps the last taps - 1 projected rows of every request as state; one kernel rotates,
 normalises and writes keys and values to their pages; the attention kernel applies the mask
-and the gate.  Angles, norms, scores and softmax are float32.
+and the gate.  Norms, scores and softmax are float32; angles are formed in float64 (their
+sines and cosines are float32).
 """
 
 from __future__ import annotations
@@ -81,7 +82,9 @@ class ConvAttentionMixer:
             inv = float(rotary["base"]) ** (-i / self.rotary_dim)
         else:
             inv = torch.zeros(1, dtype=torch.float64)
-        self.inv_freq = inv.to(torch.float32).to(ctx.device)
+        # float64: the kernel forms position * frequency and reduces it to [-pi, pi] in float64, so
+        # that the angle's error does not grow with the position
+        self.inv_freq = inv.to(ctx.device)
 
         self.qkv_width = (self.heads + self.kv_heads) * self.key_dim + self.kv_heads * self.value_dim
         self.gate_width = self.heads * self.value_dim if params.get("gate") else 0

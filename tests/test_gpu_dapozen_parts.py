@@ -172,7 +172,7 @@ def test_rotary_pairs_store(ops, dtype, geometry):
     width = (nq + nkv) * hd + nkv * vd
     qkv0 = torch.randn((batch.num_tokens, width + 5), generator=g).to(dtype).cuda()
     qkv = qkv0.clone()
-    inv = (77.0 ** (-torch.arange(0, max(rot, 2), 2, dtype=torch.float64) / max(rot, 2))).float().cuda()
+    inv = (77.0 ** (-torch.arange(0, max(rot, 2), 2, dtype=torch.float64) / max(rot, 2))).cuda()
     view = steps.mgr.view(0).paged
     group = batch.groups[0]
     ops.rotary_pairs_store(qkv, batch.positions, inv, nq, nkv, hd, vd, rot, True, 1e-5,
